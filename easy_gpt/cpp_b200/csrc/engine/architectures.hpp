@@ -3,7 +3,8 @@
 //
 // The lookup rule is the reference's (src/models/layer_key_prefix.cpp:24-28, 92-105): lower-case
 // architectures[0] and model_type; an entry matches if its key occurs in the architecture string or equals the
-// model type; no match raises an error naming both strings.  An entry turns the config.json object into a
+// model type; no match raises an error naming both strings.  (A configuration may also give the name as one string
+// under "architecture".)  An entry turns the config.json object into a
 // ModelSpec; loader, cache manager, step function, scheduler and replay need nothing else.
 #pragma once
 #include <algorithm>
@@ -37,6 +38,9 @@ struct ArchitectureRegistry {
         std::string arch, model_type;
         if (const json::Value* a = config.find("architectures"))
             if (a->is_array() && !a->array.empty() && a->array[0].is_string()) arch = a->array[0].string;
+        if (arch.empty())                                       // some configurations name it in one string
+            if (const json::Value* a = config.find("architecture"))
+                if (a->is_string()) arch = a->string;
         if (const json::Value* m = config.find("model_type"))
             if (m->is_string()) model_type = m->string;
         auto lower = [](std::string s) {
@@ -191,11 +195,141 @@ inline ModelSpec qwen2_spec(const json::Value& config) {
     return spec;
 }
 
+// ---- Gufanex ---------------------------------------------------------------------------------------------------------------
+// A decoder whose config.json lists its layers one by one: each has a mixer of its own kind and sizes ("mamba1": a
+// selective state-space mixer; "latent_attention": attention through a cached latent) and a routed feed-forward or none;
+// mixer and feed-forward read the same stream through two layer norms, x = x + (mixer(norm1(x)) + ff(norm2(x))).  A run
+// of layers ("loop": start, stop, times) is passed through several times with the same weights and a cache or state of
+// its own per pass; before every pass a learned vector of that pass is added to the stream, and before every pass but
+// the first also the stream as the embedding left it.  The output is a layer norm, the head, and a soft cap
+// c * tanh(logits / c).  Every size and constant is a key of config.json; tensor names are "l<i>.<part>.<tensor>".
+struct GufanexConfig {
+    static const json::Value& need(const json::Value& d, const std::string& key, const std::string& where) {
+        const json::Value* v = d.is_object() ? d.find(key) : nullptr;
+        if (!v || v->is_null()) throw ConfigError("config.json lacks " + where + key);
+        return *v;
+    }
+    static long long integer(const json::Value& d, const std::string& key, const std::string& where) {
+        const json::Value& v = need(d, key, where);
+        if (!v.is_number() || !v.is_integer) throw ConfigError(where + key + " must be an integer");
+        return v.integer;
+    }
+    static long long integer_or(const json::Value& d, const std::string& key, long long fallback, const std::string& where) {
+        const json::Value* v = d.is_object() ? d.find(key) : nullptr;
+        return (!v || v->is_null()) ? fallback : integer(d, key, where);
+    }
+    static double number(const json::Value& d, const std::string& key, const std::string& where) {
+        const json::Value& v = need(d, key, where);
+        if (!v.is_number()) throw ConfigError(where + key + " must be a number");
+        return v.number;
+    }
+    static bool present(const json::Value& d, const std::string& key) {
+        const json::Value* v = d.is_object() ? d.find(key) : nullptr;
+        return v && !v->is_null();
+    }
+};
+
+inline ModelSpec gufanex_spec(const json::Value& config) {
+    using C = GufanexConfig;
+    if (!config.is_object()) throw ConfigError("config.json is not a JSON object");
+    ModelSpec spec;
+    spec.architecture = "gufanex";
+    const long long width = C::integer(config, "width", ""), vocab = C::integer(config, "vocab", "");
+    if (width <= 0 || vocab <= 0) throw ConfigError("width and vocab must be > 0");
+    const double eps = C::number(C::need(config, "norm", ""), "eps", "norm.");
+    if (eps <= 0.0) throw ConfigError("norm.eps must be > 0");
+    spec.vocab_size = vocab;
+    spec.hidden_size = width;
+    spec.max_positions = C::integer_or(config, "max_positions", 1LL << 30, "");     // the design sets no limit; positions are 32-bit
+    auto layer_norm = [&](const std::string& prefix) {
+        return PartSpec{"layernorm", Params{{"size", width}, {"eps", eps}, {"weight_name", ""}, {"bias_name", ".b"}}, prefix, true};
+    };
+    const json::Value& layers = C::need(config, "layers", "");
+    if (!layers.is_array() || layers.array.empty()) throw ConfigError("layers must be a list with at least one layer");
+    for (size_t i = 0; i < layers.array.size(); ++i) {
+        const json::Value& l = layers.array[i];
+        const std::string where = "layers[" + std::to_string(i) + "].", prefix = "l" + std::to_string(i);
+        const json::Value& type = C::need(l, "type", where);
+        const json::Value& m = C::need(l, "mixer", where);
+        if (!type.is_string()) throw ConfigError(where + "type must be a string");
+        PartSpec mixer;
+        if (type.string == "mamba1") {
+            const std::string w = where + "mixer.";
+            mixer = PartSpec{"selective_scan", Params{{"hidden_size", width}, {"inner", C::integer(m, "inner", w)}, {"state", C::integer(m, "state", w)},
+                                                      {"dt_rank", C::integer(m, "dt_rank", w)}, {"conv", C::integer(m, "conv", w)}}, prefix + ".mix", true};
+        } else if (type.string == "latent_attention") {
+            const std::string w = where + "mixer.";
+            const json::Value& rot = C::need(m, "rot", w);
+            mixer = PartSpec{"latent_attention", Params{{"hidden_size", width}, {"heads", C::integer(m, "heads", w)}, {"dim", C::integer(m, "dim", w)},
+                                                        {"rot_dim", C::integer(m, "rot_dim", w)}, {"vdim", C::integer(m, "vdim", w)},
+                                                        {"kv_rank", C::integer(m, "kv_rank", w)}, {"q_rank", C::integer(m, "q_rank", w)},
+                                                        {"scale", C::number(m, "scale", w)}, {"rot_base", C::number(rot, "base", w + "rot.")},
+                                                        {"rot_dims", C::integer(rot, "dims", w + "rot.")}, {"eps", eps}, {"sink", true}}, prefix + ".mix", true};
+        } else {
+            throw ConfigError(where + "type '" + type.string + "' is no mixer of this design (mamba1, latent_attention)");
+        }
+        LayerSpec layer;
+        layer.parallel = true;
+        layer.sublayers.push_back({"mixer", mixer, layer_norm(prefix + ".norm1"), "pre", PartSpec::none()});
+        if (C::present(l, "mlp")) {
+            const json::Value& mlp = *l.find("mlp");
+            const std::string w = where + "mlp.";
+            const json::Value& kind = C::need(mlp, "kind", w);
+            if (!kind.is_string() || kind.string != "moe") throw ConfigError(w + "kind must be 'moe'");
+            const json::Value& router = C::need(mlp, "router", w);
+            const long long experts = C::integer(router, "experts", w + "router."), identity = C::integer_or(router, "identity", 0, w + "router.");
+            Params ff{{"hidden_size", width}, {"experts", experts}, {"identity", identity}, {"top", C::integer(router, "top", w + "router.")},
+                      {"ff", experts > 0 ? C::integer(C::need(mlp, "expert", w), "ff", w + "expert.") : 0LL},
+                      {"shared_ff", C::present(mlp, "shared") ? C::integer(*mlp.find("shared"), "ff", w + "shared.") : 0LL}};
+            layer.sublayers.push_back({"feed_forward", PartSpec{"routed_experts", ff, prefix + ".mlp", true}, layer_norm(prefix + ".norm2"), "pre", PartSpec::none()});
+        }
+        spec.layers.push_back(std::move(layer));
+    }
+    // the run order: the layers in front of the loop, the loop's layers `times` times (a cache or state per pass), the rest
+    const long long n = (long long)spec.layers.size();
+    long long start = n, stop = n, times = 1;
+    if (C::present(config, "loop")) {
+        const json::Value& loop = *config.find("loop");
+        start = C::integer(loop, "start", "loop.");
+        stop = C::integer(loop, "stop", "loop.");
+        times = C::integer(loop, "times", "loop.");
+        if (start < 0 || stop < start || stop > n || times < 1) throw ConfigError("loop must have 0 <= start <= stop <= layers and times >= 1");
+        if (stop > start) spec.stream_adds.push_back(PartSpec{"pass_offsets", Params{{"rows", times}, {"hidden_size", width}}, "loop.step", true});
+    }
+    int cache = 0;
+    auto run = [&](long long layer) { spec.run_order.push_back(RunEntry{(int)layer, cache++, true}); };
+    for (long long i = 0; i < std::min(start, n); ++i) run(i);
+    if (stop > start)
+        for (long long t = 0; t < times; ++t)
+            for (long long i = start; i < stop; ++i) {
+                run(i);
+                if (i == start) {
+                    RunEntry& e = spec.run_order.back();
+                    e.stream_add = 0;
+                    e.stream_add_row = (int)t;
+                    e.add_embedding = t > 0;
+                }
+            }
+    for (long long i = std::max(stop, start); i < n; ++i)
+        if (i >= stop) run(i);
+    spec.embedding = PartSpec{"embedding", Params{{"vocab_size", vocab}, {"hidden_size", width}, {"weight_name", ""}}, "embed", true};
+    spec.final_norm = layer_norm("final.norm");
+    Params head{{"vocab_size", vocab}, {"hidden_size", width}, {"weight_name", ""}};
+    if (C::present(config, "logit_softcap")) {
+        const double cap = C::number(config, "logit_softcap", "");
+        if (cap < 0.0) throw ConfigError("logit_softcap must be positive");
+        if (cap > 0.0) head.set("softcap", cap);
+    }
+    spec.lm_head = PartSpec{"lm_head", head, "head", true};
+    return spec;
+}
+
 inline void register_builtin_architectures() {
     ArchitectureRegistry& r = ArchitectureRegistry::instance();
     for (auto& e : r.entries)
         if (e.first == "qwen2") return;
     r.add("qwen2", qwen2_spec);
+    r.add("gufanex", gufanex_spec);
 }
 
 }  // namespace easygpt::engine

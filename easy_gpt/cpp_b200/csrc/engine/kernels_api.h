@@ -83,4 +83,32 @@ int eg_decode_fused_smem(int stages, int xs_bytes, int num_ops, int num_tmpls);
 // decode_fused.cu
 int eg_decode_fused(cudaStream_t stream, const void* tmpls, int num_tmpls, const void* ops, int num_ops, int tokens, int stages, int xs_bytes, int ctas,
     unsigned* sync, int* status, unsigned long long* trace);
+// layernorm.cu
+int eg_add_layernorm(cudaStream_t stream, float* residual, const void* delta_a, int dtype_a, const void* delta_b, int dtype_b, const int* rows, const float* gain1, const float* bias1, void* out1, const float* gain2, const float* bias2, void* out2, int out_dtype, int num_rows, int hidden, float eps);
+// engine_ops.cu
+int eg_stream_add(cudaStream_t stream, float* residual, const float* first, const float* offset, int tokens, int hidden);
+// engine_ops.cu
+int eg_softcap(cudaStream_t stream, float* x, long long n, float cap);
+// selective_scan.cu
+int eg_conv_silu(cudaStream_t stream, int dtype, const void* x, long long ldx, const float* conv_w, const float* conv_b, const float* state, long long slot_floats, const int* token_seq, const int* seq_starts, const int* seq_slots, void* u, long long ldu, int tokens, int channels, int taps);
+// selective_scan.cu
+int eg_conv_state(cudaStream_t stream, int dtype, const void* x, long long ldx, float* state, long long slot_floats, const int* seq_starts, const int* seq_slots, int num_seqs, int channels, int taps);
+// selective_scan.cu
+int eg_step_sizes(cudaStream_t stream, const float* low, long long ldl, const float* dw, const float* db, float* dt, int tokens, int channels, int rank);
+// selective_scan.cu
+int eg_selective_scan(cudaStream_t stream, int dtype, const void* u, long long ldu, const float* dt, const float* low, long long ldl, int b_col, int c_col, const float* A, const float* D, const void* z, long long ldz, float* state, long long slot_floats, long long state_offset, const int* seq_starts, const int* seq_slots, void* y, long long ldy, int num_seqs, int channels, int states, int states_per_lane);
+// attention_latent.cu
+int eg_latent_prepare(cudaStream_t stream, const float* down, long long ld, int q_rank, int rank, int rot, int rot_dims, const float* gain_q, const float* gain_c, float eps, const float* inv_freq, const int* positions, const int* slot_map, void* cache, int cache_dtype, int page_size, long long page_stride, long long pool_slots, void* cq, int cq_dtype, int tokens, int* status);
+// attention_latent.cu
+int eg_latent_absorb(cudaStream_t stream, int w_dtype, const float* q, long long ldq, const void* Uk, const int* positions, const float* inv_freq, int rot_dims, float scale, float* qa, int tokens, int heads, int dim, int rot, int rank);
+// attention_latent.cu
+int eg_attention_latent(cudaStream_t stream, int cache_dtype, const float* qa, const void* cache, const int* block_table, int table_stride, const int* token_seq, const int* positions, const float* sink, float* out, int tokens, int heads, int rank, int rot, int page_size, long long page_stride, int num_pages, int* status);
+// attention_latent.cu
+int eg_latent_expand(cudaStream_t stream, int w_dtype, const float* o, const void* Uv, void* out, int out_dtype, long long ldo, int tokens, int heads, int vdim, int rank);
+// moe.cu
+int eg_moe_route(cudaStream_t stream, int dtype, const void* h, long long ld, const float* router, const float* correction, const float* gate_w, int* ids, float* weights, float* gate, int tokens, int width, int outputs, int top);
+// moe.cu
+int eg_moe_hidden(cudaStream_t stream, int dtype, const void* h, long long ld, const void* gate_up, const int* ids, void* act, int tokens, int width, int ff, int top, int experts);
+// moe.cu
+int eg_moe_combine(cudaStream_t stream, int dtype, const void* h, long long ld, const void* act, const void* down, const int* ids, const float* weights, const void* shared, int shared_dtype, const float* gate, float* out, int tokens, int width, int ff, int top, int experts);
 }  // extern "C"

@@ -7,6 +7,7 @@
 
 #include "architectures.hpp"
 #include "parts.hpp"
+#include "parts_sequence.hpp"
 
 namespace easygpt::engine {
 
@@ -33,7 +34,7 @@ struct SubLayer {
 // feed-forward) run the same parts with the additions and norms as kernels of their own.
 class Block {
 public:
-    explicit Block(const LayerSpec& spec) {
+    explicit Block(const LayerSpec& spec) : parallel(spec.parallel) {
         PartRegistry& reg = PartRegistry::instance();
         if (spec.position.present) position = PartRegistry::find(reg.positions, "position", spec.position.kind)(spec.position.params, spec.position.prefix);
         auto make_norm = [&](const PartSpec& p) -> std::shared_ptr<Norm> {
@@ -62,17 +63,81 @@ public:
         return out;
     }
     // the norm that a fused add + norm in front of this layer would have to be (nullptr: nothing in front may prepare it)
-    const Norm* first_norm() const { return sublayers.front().plain_pre_norm ? sublayers.front().norm.get() : nullptr; }
+    const Norm* first_norm() const { return !parallel && sublayers.front().plain_pre_norm ? sublayers.front().norm.get() : nullptr; }
 
+    // The residual stream between layers: the buffer that holds it, a second buffer of its size, and what is still to be
+    // added to it (a part's output, or two of them behind a parallel layer; the norm that comes next adds them).
     struct Stream {
         float *residual, *spare;
-        Delta delta;
+        Delta delta, delta2;
     };
+    // adds what is pending into the residual, as kernels of their own
+    static void settle(const StepContext& ctx, Stream& s, long long n, bool all) {
+        if (s.delta2.has_delta()) {
+            launch_check(eg_add_into_f32(ctx.stream, s.residual, s.delta2.p, (int)s.delta2.dtype, n), "add");
+            s.delta2 = Delta();
+        }
+        if (all && s.delta.has_delta()) {
+            launch_check(eg_add_into_f32(ctx.stream, s.residual, s.delta.p, (int)s.delta.dtype, n), "add");
+            s.delta = Delta();
+        }
+    }
+
+    // x = x + (f1(norm1(x)) + f2(norm2(x)) + ...): every sub-layer reads the stream as it entered the layer.  The adds that
+    // the layer in front left and the first two norms are one kernel where the norms can pair up; the outputs of the
+    // first two sub-layers are handed on unadded, for the next norm to take in.
+    Stream forward_parallel(StepContext& ctx, StepArenas& arenas, int* turn, Stream s, const CacheView& cache, void* work, void* work2) const {
+        const int T = ctx.num_tokens;
+        const long long n = (long long)T * width_;
+        if (s.delta.has_pre()) throw DeviceError("prepared rows reached a parallel layer");
+        std::vector<Delta> outputs;
+        for (size_t i = 0; i < sublayers.size(); ++i) {
+            const SubLayer& sub = sublayers[i];
+            void* rows = (i & 1) ? work2 : work;
+            if (i == 0) {
+                const bool paired = sublayers.size() >= 2 &&
+                                    sub.norm->forward_pair(ctx, s.residual, s.delta.p, s.delta.dtype, s.delta2.p, s.delta2.dtype, sublayers[1].norm.get(), work, work2,
+                                                           ctx.dtype, T);
+                if (!paired) {
+                    settle(ctx, s, n, false);
+                    sub.norm->forward(ctx, s.residual, s.delta.p, s.delta.dtype, work, ctx.dtype, T, nullptr);
+                    if (sublayers.size() >= 2) sublayers[1].norm->forward(ctx, s.residual, nullptr, ctx.dtype, work2, ctx.dtype, T, nullptr);
+                }
+                s.delta = s.delta2 = Delta();
+            } else if (i >= 2) {
+                sub.norm->forward(ctx, s.residual, nullptr, ctx.dtype, rows, ctx.dtype, T, nullptr);
+            }
+            if (i >= 2) {
+                // the arena about to be reused holds the output of the sub-layer before the last: it goes into the spare buffer
+                Delta& old = outputs[i - 2];
+                if (i == 2) launch_check(eg_convert_rows(ctx.stream, old.p, (int)old.dtype, s.spare, (int)DType::F32, n), "convert");
+                else launch_check(eg_add_into_f32(ctx.stream, s.spare, old.p, (int)old.dtype, n), "add");
+                old = Delta();
+            }
+            ctx.arena = &arenas.sub[(*turn)++ & 1];
+            ctx.arena->reset();
+            PartInput in;
+            in.rows = Rows{rows, ctx.dtype, T, width_, width_};
+            Delta d = sub.mixer ? sub.mixer->forward(ctx, in, cache, nullptr) : sub.feed_forward->forward(ctx, in, nullptr);
+            if (d.has_pre()) throw DeviceError("a part returned prepared rows without having been offered the norm that follows");
+            outputs.push_back(d);
+        }
+        const size_t k = outputs.size();
+        if (k > 2) {
+            // earlier outputs were gathered in the spare buffer, which now joins the stream
+            launch_check(eg_add_into_f32(ctx.stream, s.residual, s.spare, (int)DType::F32, n), "add");
+        }
+        s.delta = outputs[k - 1];
+        if (k >= 2) s.delta2 = outputs[k - 2];
+        return s;
+    }
 
     // Returns the buffer that now holds the residual stream, the other one, and what the last sub-layer left still to be
     // added (its output, or the PreNormed it prepared for next_norm, the norm that runs after this block).
-    Stream forward(StepContext& ctx, StepArenas& arenas, int* turn, Stream s, const CacheView& cache, void* work, const Norm* next_norm) const {
+    Stream forward(StepContext& ctx, StepArenas& arenas, int* turn, Stream s, const CacheView& cache, void* work, void* work2, const Norm* next_norm) const {
         const int T = ctx.num_tokens;
+        if (parallel) return forward_parallel(ctx, arenas, turn, s, cache, work, work2);
+        settle(ctx, s, (long long)T * width_, false);
         for (size_t i = 0; i < sublayers.size(); ++i) {
             const SubLayer& sub = sublayers[i];
             // this sub-layer's arena: what the sub-layer before the last one left there is dead by now
@@ -134,6 +199,7 @@ public:
     std::vector<SubLayer> sublayers;
     std::shared_ptr<PositionEncoding> position;
     Mixer* mixer = nullptr;
+    bool parallel = false;
     int width_ = 0;                     // the model's width (for sub-layers without a norm of their own)
 };
 
@@ -149,6 +215,7 @@ class Model {
 public:
     Model(ModelSpec spec_, DType dtype) : spec(std::move(spec_)), dtype(dtype) {
         register_builtin_parts();
+        register_sequence_parts();
         spec.validate();
         PartRegistry& reg = PartRegistry::instance();
         embedding = PartRegistry::find(reg.embeddings, "embedding", spec.embedding.kind)(spec.embedding.params, spec.embedding.prefix);
@@ -159,6 +226,9 @@ public:
             blocks.emplace_back(new Block(l));
             blocks.back()->width_ = (int)spec.hidden_size;
         }
+        for (auto& a : spec.stream_adds) stream_adds.push_back(PartRegistry::find(reg.stream_adds, "stream addition", a.kind)(a.params, a.prefix));
+        for (auto& l : spec.layers) any_parallel_ = any_parallel_ || l.parallel;
+        for (auto& e : spec.run_order) keeps_embedding_ = keeps_embedding_ || e.add_embedding;
         final_norm = PartRegistry::find(reg.norms, "norm", spec.final_norm.kind)(spec.final_norm.params, spec.final_norm.prefix);
         lm_head = PartRegistry::find(reg.heads, "head", spec.lm_head.kind)(spec.lm_head.params, spec.lm_head.prefix);
     }
@@ -179,6 +249,7 @@ public:
     std::vector<Part*> all_parts() const {
         std::vector<Part*> out{embedding.get()};
         if (embedding_position) out.push_back(embedding_position.get());
+        for (auto& a : stream_adds) out.push_back(a.get());
         for (auto& b : blocks)
             for (Part* p : b->parts()) out.push_back(p);
         out.push_back(final_norm.get());
@@ -207,6 +278,7 @@ public:
         check_manifest(tensor_requests(), file);
         embedding->load(file, dtype);
         if (embedding_position) embedding_position->load(file, dtype);
+        for (auto& a : stream_adds) a->load(file, dtype);
         for (auto& b : blocks)
             for (Part* p : b->parts()) p->load(file, dtype);
         final_norm->load(file, dtype);
@@ -244,12 +316,14 @@ public:
                 head_dim = std::max(head_dim, hd);
             }
         }
+        size_t part_most = 0;
+        for (Part* p : all_parts()) part_most = std::max(part_most, p->arena_bytes(T));
         ArenaSizes sizes;
         // partial results of an attention whose keys are shared by several CTAs: capped for prompt portions, and bounded by
         // the CTAs of a few waves for single tokens
         const size_t partials = plans::PREFILL_PARTS_SCRATCH_BYTES + (size_t)(4 * plans::sm_count() + 64) * 128 * (size_t)(head_dim + 2) * 4;
-        sizes.sub = (size_t)T * (size_t)widths * 4 + partials + (4u << 20);
-        sizes.step = (size_t)T * (size_t)(3 * spec.hidden_size + std::max<long long>(head_dim, 64)) * 4 + (size_t)R * (size_t)(spec.vocab_size + spec.hidden_size) * 4 +
+        sizes.sub = std::max((size_t)T * (size_t)widths * 4, part_most) + partials + (4u << 20);
+        sizes.step = (size_t)T * (size_t)(5 * spec.hidden_size + std::max<long long>(head_dim, 64)) * 4 + (size_t)R * (size_t)(spec.vocab_size + spec.hidden_size) * 4 +
                      (4u << 20);
         return sizes;
     }
@@ -268,6 +342,7 @@ public:
         FusedProgram none;
         const int T = ctx.num_tokens;
         if (dtype != DType::BF16 || !ctx.all_decode || T <= 0 || T > EGF_MAX_TOKENS || embedding_position || spec.hidden_size % 16) return none;
+        if (any_parallel_ || !stream_adds.empty()) return none;
         FusedBuilder b;
         b.ctx = &ctx;
         arenas.reset();
@@ -318,15 +393,27 @@ public:
         s.residual = ctx.take<float>((size_t)T * H);
         s.spare = ctx.take<float>((size_t)T * H);
         void* work = ctx.take_rows(T, H, dtype);
+        void* work2 = any_parallel_ ? ctx.take_rows(T, H, dtype) : nullptr;
         embedding->forward(ctx, s.residual);
         if (embedding_position) embedding_position->add_to_embedding(s.residual, ctx);
+        float* first = nullptr;                  // the stream as the embedding left it, for the passes that add it again
+        if (keeps_embedding_) {
+            first = ctx.take<float>((size_t)T * H);
+            EG_CUDA(cudaMemcpyAsync(first, s.residual, (size_t)T * H * 4, cudaMemcpyDeviceToDevice, ctx.stream));
+        }
         const auto& order = spec.run_order;
         for (size_t i = 0; i < order.size(); ++i) {
-            const Norm* next_norm = (i + 1 < order.size()) ? blocks[order[i + 1].layer]->first_norm() : final_norm.get();
-            s = blocks[order[i].layer]->forward(ctx, arenas, &turn, s, view(order[i].cache, order[i].writes_cache), work, next_norm);
+            if (order[i].stream_add >= 0) {
+                Block::settle(ctx, s, (long long)T * H, true);
+                stream_adds[order[i].stream_add]->forward(ctx, s.residual, order[i].add_embedding ? first : nullptr, order[i].stream_add_row);
+            }
+            // the norm that the next entry starts with, unless something is added to the stream before it
+            const Norm* next_norm = (i + 1 < order.size()) ? (order[i + 1].stream_add >= 0 ? nullptr : blocks[order[i + 1].layer]->first_norm()) : final_norm.get();
+            s = blocks[order[i].layer]->forward(ctx, arenas, &turn, s, view(order[i].cache, order[i].writes_cache), work, work2, next_norm);
         }
         ctx.arena = &arenas.step;                // the head's rows and logits live for the step
         if (num_rows <= 0) return nullptr;
+        Block::settle(ctx, s, (long long)T * H, false);
         PendingNorm pending(ctx, final_norm.get(), s.residual, s.delta, s.spare, work, T, all_rows ? nullptr : logit_rows, num_rows,
                             plans::fused_norm_max_tokens(H));
         PartInput in;
@@ -345,9 +432,13 @@ public:
     DType dtype;
     std::shared_ptr<Embedding> embedding;
     std::shared_ptr<PositionEncoding> embedding_position;
+    std::vector<std::shared_ptr<StreamAdd>> stream_adds;
     std::vector<std::unique_ptr<Block>> blocks;
     std::shared_ptr<Norm> final_norm;
     std::shared_ptr<Head> lm_head;
+
+private:
+    bool any_parallel_ = false, keeps_embedding_ = false;
 };
 
 }  // namespace easygpt::engine

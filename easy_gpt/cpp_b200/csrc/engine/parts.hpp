@@ -213,6 +213,68 @@ private:
     DeviceBuffer gain_;
 };
 
+// ---- layer norm with gain and bias: y = (x - mean(x)) / sqrt(var(x) + eps) * w + b, var the mean of the squared
+// deviations, fused with the float32 residual add.  Two layer norms of the same width and eps that read the same stream
+// (a layer whose mixer and feed-forward run side by side) leave one kernel together.  Parameters: size, eps,
+// weight_name / bias_name (tensor names under the prefix; defaults ".weight" / ".bias") ---------------------------------
+class LayerNorm : public Norm {
+public:
+    LayerNorm(const Params& p, const std::string& prefix)
+        : Norm(p, prefix), size_((int)p.integer("size")), eps_((float)p.real("eps")), weight_name_(prefix + p.text("weight_name", ".weight")),
+          bias_name_(prefix + p.text("bias_name", ".bias")) {}
+    std::vector<TensorRequest> tensor_requests() const override {
+        return {TensorRequest::vector(weight_name_, size_), TensorRequest::vector(bias_name_, size_)};
+    }
+    void load(const HostTensors& file, DType) override {
+        const std::vector<float> g = host_floats(need_tensor(file, weight_name_)), b = host_floats(need_tensor(file, bias_name_));
+        gain_ = upload(g.data(), g.size(), DType::F32);
+        bias_ = upload(b.data(), b.size(), DType::F32);
+    }
+    size_t weight_bytes() const override { return (size_t)size_ * 8; }
+    bool capturable() const override { return true; }
+    void forward(const StepContext& ctx, float* residual, const void* delta, DType delta_dtype, void* out, DType out_dtype, int num_rows,
+                 const int* rows) const override {
+        launch_check(eg_add_layernorm(ctx.stream, residual, delta, (int)delta_dtype, nullptr, 0, rows, gain_.as<float>(), bias_.as<float>(), out, nullptr,
+                                      nullptr, nullptr, (int)out_dtype, num_rows, size_, eps_), "add_layernorm");
+    }
+    bool forward_pair(const StepContext& ctx, float* residual, const void* delta_a, DType dtype_a, const void* delta_b, DType dtype_b, const Norm* second,
+                      void* out, void* out2, DType out_dtype, int num_rows) const override {
+        const LayerNorm* other = dynamic_cast<const LayerNorm*>(second);
+        if (!other || other->size_ != size_ || other->eps_ != eps_) return false;
+        launch_check(eg_add_layernorm(ctx.stream, residual, delta_a, (int)dtype_a, delta_b, (int)dtype_b, nullptr, gain_.as<float>(), bias_.as<float>(), out,
+                                      other->gain_.as<float>(), other->bias_.as<float>(), out2, (int)out_dtype, num_rows, size_, eps_), "add_layernorm");
+        return true;
+    }
+    int size() const override { return size_; }
+
+private:
+    int size_;
+    float eps_;
+    std::string weight_name_, bias_name_;
+    DeviceBuffer gain_, bias_;
+};
+
+// ---- learned vectors added to the stream before a pass of a repeated run of layers: x += (first) + table[row].
+// Parameters: rows, hidden_size; the table is the tensor named by the prefix itself -----------------------------------------
+class PassOffsets : public StreamAdd {
+public:
+    PassOffsets(const Params& p, const std::string& prefix) : StreamAdd(p, prefix), rows_((int)p.integer("rows")), hidden_((int)p.integer("hidden_size")) {}
+    std::vector<TensorRequest> tensor_requests() const override { return {TensorRequest::matrix(prefix, rows_, hidden_)}; }
+    void load(const HostTensors& file, DType) override {
+        const std::vector<float> t = host_floats(need_tensor(file, prefix));
+        table_ = upload(t.data(), t.size(), DType::F32);
+    }
+    bool capturable() const override { return true; }
+    void forward(const StepContext& ctx, float* residual, const float* first, int row) const override {
+        if (row < 0 || row >= rows_) throw DeviceError("a pass names row " + std::to_string(row) + " of a table of " + std::to_string(rows_));
+        launch_check(eg_stream_add(ctx.stream, residual, first, table_.as<float>() + (size_t)row * hidden_, ctx.num_tokens, hidden_), "stream_add");
+    }
+
+private:
+    int rows_, hidden_;
+    DeviceBuffer table_;
+};
+
 // ---- rotary position encoding, half rotation over rotary_dim dimensions of each head (src/ops.cpp:404-421).  The table
 // inv_freq[k] = theta^(-2k/rotary_dim) (src/ops.cpp:172-177) is built once on the host, in double, rounded to float32 -----
 class RotaryEncoding : public PositionEncoding {
@@ -506,14 +568,17 @@ private:
 
 // ---- SwiGLU feed-forward: down( up(x) * silu(gate(x)) ) (src/models/mlp.cpp:41-49).  gate and up become one product whose
 // weight rows are interleaved (gate_0, up_0, gate_1, up_1, ...), so that every tile of the product holds both halves of the
-// outputs it covers and the activation can run in the product's epilogue.  Parameters: hidden_size, intermediate_size, bias ---
+// outputs it covers and the activation can run in the product's epilogue.  Parameters: hidden_size, intermediate_size, bias,
+// gate_name / up_name / down_name (tensor-name suffixes, by default those of the reference) ---
 class SwiGLU : public FeedForward {
 public:
     SwiGLU(const Params& p, const std::string& prefix)
-        : FeedForward(p, prefix), hidden_((int)p.integer("hidden_size")), inter_((int)p.integer("intermediate_size")), bias_(p.flag("bias", false)) {}
+        : FeedForward(p, prefix), hidden_((int)p.integer("hidden_size")), inter_((int)p.integer("intermediate_size")), bias_(p.flag("bias", false)),
+          gate_name_(prefix + p.text("gate_name", ".gate_proj.weight")), up_name_(prefix + p.text("up_name", ".up_proj.weight")),
+          down_name_(prefix + p.text("down_name", ".down_proj.weight")) {}
     std::vector<TensorRequest> tensor_requests() const override {
-        std::vector<TensorRequest> r = {TensorRequest::matrix(prefix + ".gate_proj.weight", inter_, hidden_), TensorRequest::matrix(prefix + ".up_proj.weight", inter_, hidden_),
-                                        TensorRequest::matrix(prefix + ".down_proj.weight", hidden_, inter_)};
+        std::vector<TensorRequest> r = {TensorRequest::matrix(gate_name_, inter_, hidden_), TensorRequest::matrix(up_name_, inter_, hidden_),
+                                        TensorRequest::matrix(down_name_, hidden_, inter_)};
         if (bias_) {
             r.push_back(TensorRequest::vector(prefix + ".gate_proj.bias", inter_));
             r.push_back(TensorRequest::vector(prefix + ".up_proj.bias", inter_));
@@ -522,7 +587,7 @@ public:
         return r;
     }
     void load(const HostTensors& file, DType dtype) override {
-        const std::vector<float> gate = host_floats(need_tensor(file, prefix + ".gate_proj.weight")), up = host_floats(need_tensor(file, prefix + ".up_proj.weight"));
+        const std::vector<float> gate = host_floats(need_tensor(file, gate_name_)), up = host_floats(need_tensor(file, up_name_));
         std::vector<float> w((size_t)2 * inter_ * hidden_), b;
         for (int i = 0; i < inter_; ++i) {
             std::memcpy(&w[(size_t)(2 * i) * hidden_], &gate[(size_t)i * hidden_], (size_t)hidden_ * 4);
@@ -536,7 +601,7 @@ public:
             db = host_floats(need_tensor(file, prefix + ".down_proj.bias"));
         }
         gate_up_ = Linear(w.data(), 2 * inter_, hidden_, bias_ ? b.data() : nullptr, dtype);
-        down_ = Linear(need_tensor(file, prefix + ".down_proj.weight"), bias_ ? db.data() : nullptr, dtype);
+        down_ = Linear(need_tensor(file, down_name_), bias_ ? db.data() : nullptr, dtype);
     }
     size_t weight_bytes() const override { return gate_up_.weight_bytes() + down_.weight_bytes(); }
     bool capturable() const override { return true; }
@@ -608,16 +673,18 @@ public:
 private:
     int hidden_, inter_;
     bool bias_;
+    std::string gate_name_, up_name_, down_name_;      // the weights' tensor names (parameters gate_name / up_name / down_name: suffixes of the prefix)
     Linear gate_up_, down_;
 };
 
 // ---- token embedding: residual[t] = E[id[t]] (src/models/embedding.cpp:54-76) ---------------------------------------
 class TokenEmbedding : public Embedding {
 public:
-    TokenEmbedding(const Params& p, const std::string& prefix) : Embedding(p, prefix), vocab_((int)p.integer("vocab_size")), hidden_((int)p.integer("hidden_size")) {}
-    std::vector<TensorRequest> tensor_requests() const override { return {TensorRequest::matrix(prefix + ".weight", vocab_, hidden_)}; }
+    TokenEmbedding(const Params& p, const std::string& prefix)
+        : Embedding(p, prefix), vocab_((int)p.integer("vocab_size")), hidden_((int)p.integer("hidden_size")), weight_name_(prefix + p.text("weight_name", ".weight")) {}
+    std::vector<TensorRequest> tensor_requests() const override { return {TensorRequest::matrix(weight_name_, vocab_, hidden_)}; }
     void load(const HostTensors& file, DType dtype) override {
-        table_ = upload(need_tensor(file, prefix + ".weight"), dtype);
+        table_ = upload(need_tensor(file, weight_name_), dtype);
         dtype_ = dtype;
     }
     bool capturable() const override { return true; }
@@ -635,29 +702,35 @@ public:
 
 private:
     int vocab_, hidden_;
+    std::string weight_name_;
     DType dtype_ = DType::BF16;
     DeviceBuffer table_;
 };
 
 // ---- output head: logits = x E^T when tied (the reference always is, src/models/gpt_model.cpp:324-328,
 // src/models/embedding.cpp:78-81) or x W_head^T with lm_head.weight when not.  Logits are float32 in both precisions.
-// Parameters: vocab_size, hidden_size, tied_to (prefix of the embedding, or absent) -------------------------------------
+// Parameters: vocab_size, hidden_size, tied_to (prefix of the embedding, or absent), weight_name (suffix, default
+// ".weight"), softcap (c > 0: logits <- c tanh(logits / c)) -------------------------------------
 class LMHead : public Head {
 public:
-    LMHead(const Params& p, const std::string& prefix) : Head(p, prefix), vocab_((int)p.integer("vocab_size")), hidden_((int)p.integer("hidden_size")), tied_(p.has("tied_to")) {}
+    LMHead(const Params& p, const std::string& prefix)
+        : Head(p, prefix), vocab_((int)p.integer("vocab_size")), hidden_((int)p.integer("hidden_size")), tied_(p.has("tied_to")),
+          softcap_(p.has("softcap") ? (float)p.real("softcap") : 0.f), weight_name_(prefix + p.text("weight_name", ".weight")) {
+        if (softcap_ < 0.f) throw std::invalid_argument("softcap must be positive");
+    }
     std::vector<TensorRequest> tensor_requests() const override {
         if (tied_) return {};
-        return {TensorRequest::matrix(prefix + ".weight", vocab_, hidden_)};
+        return {TensorRequest::matrix(weight_name_, vocab_, hidden_)};
     }
     void load_head(const HostTensors& file, DType dtype, const void* tied_table) override {
         if (tied_) linear_ = Linear::sharing(tied_table, vocab_, hidden_, dtype);
-        else linear_ = Linear(need_tensor(file, prefix + ".weight"), nullptr, dtype);
+        else linear_ = Linear(need_tensor(file, weight_name_), nullptr, dtype);
     }
     size_t weight_bytes() const override { return linear_.weight_bytes(); }
     bool capturable() const override { return true; }
     int vocab() const override { return vocab_; }
     bool emit_fused(FusedBuilder& b, const float* gain, float eps) const override {
-        if (b.ctx->dtype != DType::BF16 || hidden_ != b.hidden || linear_.has_bias()) return false;
+        if (b.ctx->dtype != DType::BF16 || hidden_ != b.hidden || linear_.has_bias() || softcap_ > 0.f) return false;
         b.logits = b.arena->take_n<float>((size_t)b.tokens * vocab_);
         EgFusedTemplate t = FusedBuilder::blank();
         t.input = EGF_IN_NORM;
@@ -678,12 +751,17 @@ public:
         // product: the norm runs once, in a kernel of its own.
         Rows x = in.pending ? in.pending->materialize() : in.rows;
         x.rows = rows;
-        return (float*)linear_(ctx, x, /*out_f32=*/true).p;
+        float* logits = (float*)linear_(ctx, x, /*out_f32=*/true).p;
+        // logits <- cap * tanh(logits / cap), where the model has such a cap
+        if (softcap_ > 0.f) launch_check(eg_softcap(ctx.stream, logits, (long long)rows * vocab_, softcap_), "softcap");
+        return logits;
     }
 
 private:
     int vocab_, hidden_;
     bool tied_;
+    float softcap_;
+    std::string weight_name_;
     Linear linear_;
 };
 
@@ -695,6 +773,8 @@ inline void register_builtin_parts() {
     };
     r.feed_forwards["swiglu"] = [](const Params& p, const std::string& prefix) { return std::make_shared<SwiGLU>(p, prefix); };
     r.norms["rmsnorm"] = [](const Params& p, const std::string& prefix) { return std::make_shared<RMSNorm>(p, prefix); };
+    r.norms["layernorm"] = [](const Params& p, const std::string& prefix) { return std::make_shared<LayerNorm>(p, prefix); };
+    r.stream_adds["pass_offsets"] = [](const Params& p, const std::string& prefix) { return std::make_shared<PassOffsets>(p, prefix); };
     r.positions["rope"] = [](const Params& p, const std::string& prefix) { return std::make_shared<RotaryEncoding>(p, prefix); };
     r.embeddings["embedding"] = [](const Params& p, const std::string& prefix) { return std::make_shared<TokenEmbedding>(p, prefix); };
     r.heads["lm_head"] = [](const Params& p, const std::string& prefix) { return std::make_shared<LMHead>(p, prefix); };

@@ -35,11 +35,12 @@ namespace easygpt::engine {
 struct CacheNeed {
     enum Kind { None, PagedKV, State } kind = None;
     int num_kv_heads = 0, head_dim = 0;
+    int planes = 2;                         // PagedKV: 2 = keys and values; 1 = one row per token (a latent that serves as both)
     long long window = -1;                  // PagedKV: < 0 keeps all keys
     std::vector<long long> state_shape;     // State: a tensor of this shape per live request, zeroed when a request starts
     DType state_dtype = DType::F32;
     bool operator==(const CacheNeed& o) const {
-        return kind == o.kind && num_kv_heads == o.num_kv_heads && head_dim == o.head_dim && window == o.window &&
+        return kind == o.kind && num_kv_heads == o.num_kv_heads && head_dim == o.head_dim && planes == o.planes && window == o.window &&
                state_shape == o.state_shape && state_dtype == o.state_dtype;
     }
     static CacheNeed paged(int kv_heads, int head_dim, long long window) {
@@ -48,6 +49,12 @@ struct CacheNeed {
         n.num_kv_heads = kv_heads;
         n.head_dim = head_dim;
         n.window = window;
+        return n;
+    }
+    // one row of `width` values per token, shared by all heads
+    static CacheNeed paged_rows(int width, long long window) {
+        CacheNeed n = paged(1, width, window);
+        n.planes = 1;
         return n;
     }
     static CacheNeed state(std::vector<long long> shape, DType dtype = DType::F32) {
@@ -137,6 +144,9 @@ public:
     // takes this part's tensors (host, stored precision) to the device in the form its kernels want
     virtual void load(const HostTensors&, DType) {}
     virtual size_t weight_bytes() const { return 0; }       // bytes of weights one forward reads (roofline arithmetic)
+    // bytes of arena memory one forward over `tokens` tokens takes at most (0: the model's own estimate from the part's
+    // parameters covers it)
+    virtual size_t arena_bytes(long long /*tokens*/) const { return 0; }
     // true if forward() only launches device work whose shape depends on the batch's size alone (no reads of the
     // batch's contents on the host): then decode steps may be captured in a CUDA graph
     virtual bool capturable() const { return false; }
@@ -172,7 +182,21 @@ public:
     // With rows only those rows are normalised, into out[0 .. num_rows), and the residual is left as it is.
     virtual void forward(const StepContext& ctx, float* residual, const void* delta, DType delta_dtype, void* out, DType out_dtype, int num_rows,
                          const int* rows) const = 0;
+    // residual += delta_a + delta_b (either may be null), out = this norm's rows and out2 = `second`'s rows of the same
+    // sum, in one kernel; false: this norm cannot (the caller adds and normalises step by step)
+    virtual bool forward_pair(const StepContext& /*ctx*/, float* /*residual*/, const void* /*delta_a*/, DType /*dtype_a*/, const void* /*delta_b*/,
+                              DType /*dtype_b*/, const Norm* /*second*/, void* /*out*/, void* /*out2*/, DType /*out_dtype*/, int /*num_rows*/) const {
+        return false;
+    }
     virtual int size() const = 0;
+};
+
+// Something added to the residual stream between layers (before a pass of a repeated run of layers, say).
+class StreamAdd : public Part {
+public:
+    using Part::Part;
+    // residual [T, hidden] += first (the stream as the embedding left it, or null) + this part's vector number `row`
+    virtual void forward(const StepContext& ctx, float* residual, const float* first, int row) const = 0;
 };
 
 // Left by a part in place of its delta when it took a FollowingNorm over: the residual already holds the sum v;
@@ -410,6 +434,7 @@ struct PartRegistry {
     std::map<std::string, Factory<PositionEncoding>> positions;
     std::map<std::string, Factory<Embedding>> embeddings;
     std::map<std::string, Factory<Head>> heads;
+    std::map<std::string, Factory<StreamAdd>> stream_adds;
 
     static PartRegistry& instance() {
         static PartRegistry r;

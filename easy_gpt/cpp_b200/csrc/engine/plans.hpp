@@ -154,4 +154,19 @@ inline bool gemm_tcgen05_wide_takes(DType dtype, int tokens, int out_features, i
            (long long)((tokens + 127) / 128) * (out_features / 256) >= sm_count();
 }
 
+// How many of a channel's states one thread of the selective scan keeps (1, 2, 4, ... 32): as many as still leave a
+// block of threads for every SM when one request is scanned alone.  It hangs off the mixer's sizes alone, never off the
+// batch, so the order of the sum over a channel's states is the same in every step.
+inline int scan_states_per_lane(int channels, int states) {
+    int spl = 32;
+    while (spl > 1) {
+        int lanes = 1;
+        while (lanes * spl < states) lanes <<= 1;
+        if ((long long)channels * lanes >= 128LL * sm_count()) break;
+        spl >>= 1;
+    }
+    while ((states + spl - 1) / spl > 32) spl *= 2;
+    return spl;
+}
+
 }  // namespace easygpt::engine::plans

@@ -101,6 +101,9 @@ struct SubLayerSpec {
 struct LayerSpec {
     std::vector<SubLayerSpec> sublayers;
     PartSpec position = PartSpec::none();     // handed to the layer's mixer
+    // parallel: every sub-layer reads the stream as it entered the layer, x = x + (f1(norm1(x)) + f2(norm2(x)) + ...);
+    // each sub-layer then has a norm in front ("pre") and none behind
+    bool parallel = false;
 
     // the common block x += mixer(norm1(x)); x += feed_forward(norm2(x))
     static LayerSpec pre_norm(PartSpec mixer, PartSpec feed_forward, PartSpec mixer_norm, PartSpec feed_forward_norm, PartSpec position) {
@@ -114,10 +117,16 @@ struct LayerSpec {
 
 // One line of the run order: `layer` indexes ModelSpec::layers (a layer may be named more than once: its
 // weights are shared); entries with the same `cache` share it and only the one with writes_cache appends.
+// Before the entry's layer runs, something may be added to the stream: `stream_add` indexes ModelSpec::stream_adds (a
+// part with a table of learned vectors, of which the entry names row `stream_add_row`), and with add_embedding the
+// stream as the embedding left it is added first.
 struct RunEntry {
     int layer;
     int cache;
     bool writes_cache = true;
+    int stream_add = -1;
+    int stream_add_row = 0;
+    bool add_embedding = false;
 };
 
 struct ModelSpec {
@@ -127,6 +136,7 @@ struct ModelSpec {
     std::vector<RunEntry> run_order;
     PartSpec embedding, final_norm, lm_head;
     PartSpec embedding_position = PartSpec::none();
+    std::vector<PartSpec> stream_adds;
     long long bos_token_id = -1, eos_token_id = -1;
 
     void validate() const {
@@ -136,6 +146,10 @@ struct ModelSpec {
             if (e.layer < 0 || e.layer >= (int)layers.size())
                 throw std::invalid_argument("run order entry " + std::to_string(i) + " names layer " + std::to_string(e.layer) + ", but there are " +
                                             std::to_string(layers.size()) + " layers");
+            if (e.stream_add >= (int)stream_adds.size())
+                throw std::invalid_argument("run order entry " + std::to_string(i) + " names stream addition " + std::to_string(e.stream_add) + ", but there are " +
+                                            std::to_string(stream_adds.size()));
+            if (e.add_embedding && e.stream_add < 0) throw std::invalid_argument("run order entry " + std::to_string(i) + " adds the embedding without a stream addition");
             if (e.writes_cache) {
                 if (owner.count(e.cache))
                     throw std::invalid_argument("cache " + std::to_string(e.cache) + " is written by run entries " + std::to_string(owner[e.cache]) +
@@ -157,6 +171,8 @@ struct ModelSpec {
                 if (s.role != "mixer" && s.role != "feed_forward") throw std::invalid_argument("a sub-layer's role is 'mixer' or 'feed_forward', not '" + s.role + "'");
                 if (s.norm_placement != "pre" && s.norm_placement != "post") throw std::invalid_argument("norm_placement is 'pre' or 'post'");
                 mixers += s.role == "mixer";
+                if (l.parallel && (!s.norm.present || s.norm_placement != "pre" || s.output_norm.present))
+                    throw std::invalid_argument("a parallel layer's sub-layers each have a norm in front and none behind");
             }
             if (mixers > 1) throw std::invalid_argument("a layer has at most one mixer");
         }

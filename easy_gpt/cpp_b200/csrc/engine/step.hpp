@@ -1,8 +1,8 @@
 // The cache manager's device side and the step function.
 //
 // DeviceCache: the bookkeeping of csrc/host/cache_core.hpp (pages, block tables, slots) with the device memory it
-// addresses: per group of caches with the same needs one tensor [caches, pages + 1, 2 (k, v), kv_heads, page_size,
-// head_dim] in the engine's dtype (the extra page is the scratch page that padding rows of a captured batch write
+// addresses: per group of caches with the same needs one tensor [caches, pages + 1, planes (k, v; or one row per token
+// that serves as both), kv_heads, page_size, head_dim] in the engine's dtype (the extra page is the scratch page that padding rows of a captured batch write
 // to), and per cache that asked for fixed-size state one tensor [slots + 1, elements], zeroed when a request takes a slot
 // (the extra slot is the scratch slot that padding rows of a captured batch use).
 //
@@ -79,7 +79,7 @@ public:
                     g->need = need;
                     g->num_pages = num_pages;
                     g->scratch_page = num_pages;
-                    g->layer_elems = (size_t)(num_pages + 1) * 2 * need.num_kv_heads * page_size * need.head_dim;
+                    g->layer_elems = (size_t)(num_pages + 1) * need.planes * need.num_kv_heads * page_size * need.head_dim;
                 }
                 g->cache_ids.push_back(kv.first);
                 group_of_cache[kv.first] = g->index;
@@ -108,8 +108,8 @@ public:
             const long long plane = (long long)g.need.num_kv_heads * page_size * g.need.head_dim;
             v.group = g.index;
             v.k = base;
-            v.v = base + (size_t)plane * es;
-            v.page_stride = 2 * plane;
+            v.v = g.need.planes == 2 ? base + (size_t)plane * es : nullptr;
+            v.page_stride = g.need.planes * plane;
             v.head_stride = (long long)page_size * g.need.head_dim;
             v.num_pages = g.num_pages + 1;
             v.page_size = page_size;
@@ -133,7 +133,7 @@ public:
     }
     size_t kv_bytes_per_token() const {
         size_t total = 0;
-        for (auto& g : groups) total += g->cache_ids.size() * 2 * g->need.num_kv_heads * g->need.head_dim * dtype_size(dtype);
+        for (auto& g : groups) total += g->cache_ids.size() * g->need.planes * g->need.num_kv_heads * g->need.head_dim * dtype_size(dtype);
         return total;
     }
 

@@ -35,3 +35,34 @@ EG_API int eg_convert_rows(cudaStream_t stream, const void* src, int src_dtype, 
     else convert_rows_kernel<bf16, bf16><<<blocks, 256, 0, stream>>>((const bf16*)src, (bf16*)dst, n);
     return eg_launch_status();
 }
+
+namespace {
+// residual[t, j] = (residual[t, j] + first[t, j]) + offset[j]
+__global__ void stream_add_kernel(float* __restrict__ residual, const float* __restrict__ first, const float* __restrict__ offset, long long n, int hidden) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    float v = residual[i];
+    if (first) v += first[i];
+    residual[i] = v + offset[i % hidden];
+}
+__global__ void softcap_kernel(float* __restrict__ x, long long n, float cap, float inv_cap) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) x[i] = cap * tanhf(x[i] * inv_cap);
+}
+}  // namespace
+
+// What a repeated run of layers adds to the stream before a pass: residual [tokens, hidden] += first (the stream as the
+// embedding left it; may be null) and += offset [hidden] (a learned vector of the pass), in that order, in float32.
+EG_API int eg_stream_add(cudaStream_t stream, float* residual, const float* first, const float* offset, int tokens, int hidden) {
+    const long long n = (long long)tokens * hidden;
+    if (n <= 0) return 0;
+    stream_add_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(residual, first, offset, n, hidden);
+    return eg_launch_status();
+}
+
+// x[i] = cap * tanh(x[i] / cap), i < n (float32, accurate tanh)
+EG_API int eg_softcap(cudaStream_t stream, float* x, long long n, float cap) {
+    if (n <= 0) return 0;
+    softcap_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(x, n, cap, 1.0f / cap);
+    return eg_launch_status();
+}

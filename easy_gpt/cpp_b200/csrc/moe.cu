@@ -1,0 +1,169 @@
+// A routed feed-forward: a router that picks `top` of the experts per token, gated experts, experts that hand their
+// input through unchanged, and a gate on a shared expert.
+//
+//   eg_moe_route     logits = R h (float32); s = softmax(logits) over all router outputs; the `top` largest of
+//                    s + correction are chosen (ties: the lower index); their weights are s itself, not renormalised.
+//                    Also g[t] = sigmoid(w_g . h), the gate of the shared expert, when w_g is given.
+//   eg_moe_hidden    a[t, k, :] = silu(G_e h) * (U_e h) for the k-th chosen expert e of token t (skipped for router
+//                    outputs >= experts: those stand for the identity)
+//   eg_moe_combine   out[t, :] = sum_k weight[t, k] * (D_e a[t, k, :]  or  h[t, :] for an identity choice)
+//                                + g[t] * shared[t, :]                   (float32)
+//
+// eg_moe_hidden and eg_moe_combine read each chosen expert's weights per token: the form for steps of few tokens.
+// Products accumulate in float32; the router is float32 throughout.
+#include "common.cuh"
+
+namespace {
+
+// one block of four warps per token
+template <typename T>
+__global__ void __launch_bounds__(128) moe_route_kernel(const T* __restrict__ h, long long ld, const float* __restrict__ router,
+                                                        const float* __restrict__ correction, const float* __restrict__ gate_w, int* __restrict__ ids,
+                                                        float* __restrict__ weights, float* __restrict__ gate, int width, int outputs, int top) {
+    extern __shared__ float sm[];                // [width] the token's row, [outputs] logits, then scores
+    float* row = sm;
+    float* logit = sm + width;
+    const int t = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int j = threadIdx.x; j < width; j += blockDim.x) row[j] = to_f32<T>(h[(size_t)t * ld + j]);
+    __syncthreads();
+    for (int e = warp; e < outputs + (gate_w ? 1 : 0); e += 4) {
+        const float* w = e < outputs ? router + (size_t)e * width : gate_w;
+        float acc = 0.f;
+        for (int j = lane; j < width; j += 32) acc = fmaf(w[j], row[j], acc);
+        acc = warp_sum(acc);
+        if (lane == 0) {
+            if (e < outputs) logit[e] = acc;
+            else gate[t] = 1.0f / (1.0f + expf(-acc));
+        }
+    }
+    __syncthreads();
+    if (warp != 0) return;
+    float top_logit = -INFINITY;
+    for (int e = lane; e < outputs; e += 32) top_logit = fmaxf(top_logit, logit[e]);
+    top_logit = warp_max(top_logit);
+    float sum = 0.f;
+    for (int e = lane; e < outputs; e += 32) sum += expf(logit[e] - top_logit);
+    sum = warp_sum(sum);
+    for (int e = lane; e < outputs; e += 32) logit[e] = expf(logit[e] - top_logit) / sum;      // now the scores s
+    __syncwarp();
+    unsigned long long taken_lo = 0ull;          // lanes track which of their own outputs are taken: bit k for e = lane + 32 k
+    for (int k = 0; k < top; ++k) {
+        float best = -INFINITY;
+        int arg = 0x7fffffff;
+        for (int e = lane, i = 0; e < outputs; e += 32, ++i) {
+            if (i < 64 && (taken_lo >> i) & 1ull) continue;
+            const float v = logit[e] + correction[e];
+            if (v > best) { best = v; arg = e; }
+        }
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+            if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
+        }
+        if (arg != 0x7fffffff && arg % 32 == lane) taken_lo |= 1ull << (arg / 32);
+        if (lane == 0) {
+            ids[(size_t)t * top + k] = arg == 0x7fffffff ? outputs : arg;
+            weights[(size_t)t * top + k] = arg == 0x7fffffff ? 0.f : logit[arg];
+        }
+    }
+}
+
+// grid (token, choice, chunk of ff); a warp per hidden unit; GU [experts, 2 ff, width] with the gate row of unit f at
+// 2 f and its up row at 2 f + 1
+template <typename T>
+__global__ void __launch_bounds__(256) moe_hidden_kernel(const T* __restrict__ h, long long ld, const T* __restrict__ GU, const int* __restrict__ ids,
+                                                         T* __restrict__ act, int width, int ff, int top, int experts) {
+    extern __shared__ float row[];
+    const int t = blockIdx.x, k = blockIdx.y;
+    const int e = ids[(size_t)t * top + k];
+    if (e >= experts) return;
+    for (int j = threadIdx.x; j < width; j += blockDim.x) row[j] = to_f32<T>(h[(size_t)t * ld + j]);
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+    const int f = blockIdx.z * warps + warp;
+    if (f >= ff) return;
+    const T* g = GU + ((size_t)e * 2 * ff + 2 * f) * width;
+    const T* u = g + width;
+    float ag = 0.f, au = 0.f;
+    for (int j = lane; j < width; j += 32) {
+        ag = fmaf(to_f32<T>(g[j]), row[j], ag);
+        au = fmaf(to_f32<T>(u[j]), row[j], au);
+    }
+    ag = warp_sum(ag);
+    au = warp_sum(au);
+    if (lane == 0) act[((size_t)t * top + k) * ff + f] = from_f32<T>(ag / (1.0f + expf(-ag)) * au);
+}
+
+// grid (token, chunk of width); a warp per output value; Dn [experts, width, ff]
+template <typename T>
+__global__ void __launch_bounds__(256) moe_combine_kernel(const T* __restrict__ h, long long ld, const T* __restrict__ act, const T* __restrict__ Dn,
+                                                          const int* __restrict__ ids, const float* __restrict__ weights, const void* __restrict__ shared,
+                                                          int shared_dtype, const float* __restrict__ gate, float* __restrict__ out, int width, int ff,
+                                                          int top, int experts) {
+    const int t = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+    const int j = blockIdx.y * warps + warp;
+    if (j >= width) return;
+    float total = 0.f;
+    for (int k = 0; k < top; ++k) {
+        const int e = ids[(size_t)t * top + k];
+        const float wgt = weights[(size_t)t * top + k];
+        if (e >= experts) {
+            total += wgt * to_f32<T>(h[(size_t)t * ld + j]);
+            continue;
+        }
+        const T* d = Dn + ((size_t)e * width + j) * ff;
+        const T* a = act + ((size_t)t * top + k) * ff;
+        float acc = 0.f;
+        for (int f = lane; f < ff; f += 32) acc = fmaf(to_f32<T>(d[f]), to_f32<T>(a[f]), acc);
+        total += wgt * warp_sum(acc);
+    }
+    if (shared) {
+        const size_t i = (size_t)t * width + j;
+        total += gate[t] * (shared_dtype == EG_BF16 ? __bfloat162float(((const bf16*)shared)[i]) : ((const float*)shared)[i]);
+    }
+    if (lane == 0) out[(size_t)t * width + j] = total;
+}
+
+}  // namespace
+
+// ids [T, top] int32 (>= experts... see eg_moe_hidden), weights [T, top] float32, gate [T] float32 (only with gate_w)
+EG_API int eg_moe_route(cudaStream_t stream, int dtype, const void* h, long long ld, const float* router, const float* correction, const float* gate_w,
+                        int* ids, float* weights, float* gate, int tokens, int width, int outputs, int top) {
+    if (tokens <= 0) return 0;
+    const size_t smem = (size_t)(width + outputs) * sizeof(float);
+    if (top < 1 || top > outputs || outputs > 2048 || smem > 48 * 1024) return (int)cudaErrorInvalidValue;
+    if (dtype == EG_BF16)
+        moe_route_kernel<bf16><<<tokens, 128, smem, stream>>>((const bf16*)h, ld, router, correction, gate_w, ids, weights, gate, width, outputs, top);
+    else
+        moe_route_kernel<float><<<tokens, 128, smem, stream>>>((const float*)h, ld, router, correction, gate_w, ids, weights, gate, width, outputs, top);
+    return eg_launch_status();
+}
+
+// act [T, top, ff] in the compute dtype; rows of identity choices (ids >= experts) are left untouched
+EG_API int eg_moe_hidden(cudaStream_t stream, int dtype, const void* h, long long ld, const void* gate_up, const int* ids, void* act, int tokens,
+                         int width, int ff, int top, int experts) {
+    if (tokens <= 0 || experts <= 0) return 0;
+    const size_t smem = (size_t)width * sizeof(float);
+    if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
+    dim3 grid(tokens, top, (ff + 7) / 8);
+    if (dtype == EG_BF16) moe_hidden_kernel<bf16><<<grid, 256, smem, stream>>>((const bf16*)h, ld, (const bf16*)gate_up, ids, (bf16*)act, width, ff, top, experts);
+    else moe_hidden_kernel<float><<<grid, 256, smem, stream>>>((const float*)h, ld, (const float*)gate_up, ids, (float*)act, width, ff, top, experts);
+    return eg_launch_status();
+}
+
+// out [T, width] float32; shared [T, width] (shared_dtype) with gate [T], or null
+EG_API int eg_moe_combine(cudaStream_t stream, int dtype, const void* h, long long ld, const void* act, const void* down, const int* ids,
+                          const float* weights, const void* shared, int shared_dtype, const float* gate, float* out, int tokens, int width, int ff,
+                          int top, int experts) {
+    if (tokens <= 0) return 0;
+    dim3 grid(tokens, (width + 7) / 8);
+    if (dtype == EG_BF16)
+        moe_combine_kernel<bf16><<<grid, 256, 0, stream>>>((const bf16*)h, ld, (const bf16*)act, (const bf16*)down, ids, weights, shared, shared_dtype, gate,
+                                                          out, width, ff, top, experts);
+    else
+        moe_combine_kernel<float><<<grid, 256, 0, stream>>>((const float*)h, ld, (const float*)act, (const float*)down, ids, weights, shared, shared_dtype,
+                                                           gate, out, width, ff, top, experts);
+    return eg_launch_status();
+}

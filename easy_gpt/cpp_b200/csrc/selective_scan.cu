@@ -1,0 +1,205 @@
+// The kernels of a selective state-space mixer (a causal convolution per channel, input-dependent step sizes, and a
+// diagonal linear recurrence per channel and state) over a mixed batch: every entry of the batch is a run of tokens of
+// one request that continues from the request's state slot.
+//
+// Per request the slot holds, in float32: the last taps-1 inputs of the convolution [taps-1, channels], then the
+// recurrent state S [channels, states].  A slot is zero when a request first takes it, which is the convolution's
+// zeros before the sequence and S = 0.
+//
+//   u[t, c]  = silu(cb[c] + sum_j cw[c, j] * x[t - (taps-1) + j, c])            (the last tap weighs the current token)
+//   dt[t, c] = softplus(db[c] + sum_r dw[c, r] * low[t, r])                     (float32)
+//   S[c, n] <- exp(dt[t, c] * A[c, n]) * S[c, n] + dt[t, c] * u[t, c] * B[t, n] (float32)
+//   y[t, c]  = (sum_n S[c, n] * C[t, n] + D[c] * u[t, c]) * silu(z[t, c])
+//
+// Decays, step sizes, exponentials and the state are float32 in both precisions; the convolution's inputs and outputs
+// are in the compute dtype with float32 sums.
+#include "common.cuh"
+
+namespace {
+
+__device__ __forceinline__ float silu_f(float v) { return v / (1.0f + expf(-v)); }
+__device__ __forceinline__ float softplus_f(float v) { return v > 20.0f ? v : log1pf(expf(v)); }
+
+// one thread per (token, channel)
+template <typename T>
+__global__ void conv_silu_kernel(const T* __restrict__ x, long long ldx, const float* __restrict__ cw, const float* __restrict__ cb,
+                                 const float* __restrict__ state, long long slot_floats, const int* __restrict__ token_seq,
+                                 const int* __restrict__ seq_starts, const int* __restrict__ seq_slots, T* __restrict__ u, long long ldu, int tokens,
+                                 int channels, int taps) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long long)tokens * channels) return;
+    const int t = (int)(i / channels), c = (int)(i % channels);
+    const int seq = token_seq[t], start = seq_starts[seq];
+    const float* past = state + (size_t)seq_slots[seq] * slot_floats;
+    float acc = cb[c];
+    for (int j = 0; j < taps; ++j) {
+        const int src = t - (taps - 1) + j;
+        // before the entry's first token: the request's earlier inputs, the newest of which is row taps-2 of the slot
+        const float v = src >= start ? to_f32<T>(x[(size_t)src * ldx + c]) : past[(size_t)(taps - 1 + src - start) * channels + c];
+        acc = fmaf(cw[(size_t)c * taps + j], v, acc);
+    }
+    u[(size_t)t * ldu + c] = from_f32<T>(silu_f(acc));
+}
+
+// one thread per (entry, channel): the slot's rows become the last taps-1 inputs of the request after this step
+template <typename T>
+__global__ void conv_state_kernel(const T* __restrict__ x, long long ldx, float* __restrict__ state, long long slot_floats,
+                                  const int* __restrict__ seq_starts, const int* __restrict__ seq_slots, int num_seqs, int channels, int taps) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long long)num_seqs * channels) return;
+    const int seq = (int)(i / channels), c = (int)(i % channels);
+    const int start = seq_starts[seq], n = seq_starts[seq + 1] - start;
+    float* past = state + (size_t)seq_slots[seq] * slot_floats;
+    for (int r = 0; r < taps - 1; ++r) {                    // ascending: row r + n is read before any row >= r + 1 is written
+        const int src = n - (taps - 1) + r;
+        past[(size_t)r * channels + c] = src >= 0 ? to_f32<T>(x[(size_t)(start + src) * ldx + c]) : past[(size_t)(r + n) * channels + c];
+    }
+}
+
+// one thread per (token, channel); low [tokens, ldl] float32, dw [channels, rank] float32
+__global__ void step_size_kernel(const float* __restrict__ low, long long ldl, const float* __restrict__ dw, const float* __restrict__ db,
+                                 float* __restrict__ dt, int tokens, int channels, int rank) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long long)tokens * channels) return;
+    const int t = (int)(i / channels), c = (int)(i % channels);
+    float acc = db[c];
+    for (int r = 0; r < rank; ++r) acc = fmaf(dw[(size_t)c * rank + r], low[(size_t)t * ldl + r], acc);
+    dt[i] = softplus_f(acc);
+}
+
+// The recurrence.  LANES threads share a channel; a thread keeps SPL states (n = lane + LANES * k) in registers for the
+// whole run of tokens, so that a step costs its exponentials and two fused multiply-adds per state, and the sum over the
+// states is LANES' shuffle steps.  A block covers blockDim.x / LANES channels of one entry.
+template <typename T, int SPL>
+__global__ void __launch_bounds__(128) selective_scan_kernel(const T* __restrict__ u, long long ldu, const float* __restrict__ dt,
+                                                             const float* __restrict__ low, long long ldl, int b_col, int c_col,
+                                                             const float* __restrict__ A, const float* __restrict__ D, const T* __restrict__ z,
+                                                             long long ldz, float* __restrict__ state, long long slot_floats, long long state_offset,
+                                                             const int* __restrict__ seq_starts, const int* __restrict__ seq_slots, T* __restrict__ y,
+                                                             long long ldy, int channels, int states, int lanes) {
+    const int seq = blockIdx.y;
+    const int lane = threadIdx.x % lanes;
+    const int c = blockIdx.x * (blockDim.x / lanes) + threadIdx.x / lanes;
+    const bool live = c < channels;
+    const int cc = live ? c : channels - 1;
+    float* S = state + (size_t)seq_slots[seq] * slot_floats + state_offset + (size_t)cc * states;
+    float s[SPL], a[SPL];
+#pragma unroll
+    for (int k = 0; k < SPL; ++k) {
+        const int n = lane + lanes * k;
+        s[k] = n < states ? S[n] : 0.f;
+        a[k] = n < states ? A[(size_t)cc * states + n] : 0.f;
+    }
+    const float d_skip = D[cc];
+    const int t0 = seq_starts[seq], t1 = seq_starts[seq + 1];
+    for (int t = t0; t < t1; ++t) {
+        const float step = dt[(size_t)t * channels + cc];
+        const float in = to_f32<T>(u[(size_t)t * ldu + cc]);
+        const float drive = step * in;
+        const float* Bt = low + (size_t)t * ldl + b_col;
+        const float* Ct = low + (size_t)t * ldl + c_col;
+        float acc = 0.f;
+#pragma unroll
+        for (int k = 0; k < SPL; ++k) {
+            const int n = lane + lanes * k;
+            if (n < states) {
+                s[k] = fmaf(expf(step * a[k]), s[k], drive * Bt[n]);
+                acc = fmaf(s[k], Ct[n], acc);
+            }
+        }
+        for (int o = lanes >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+        if (lane == 0 && live) {
+            const float gate = to_f32<T>(z[(size_t)t * ldz + c]);
+            y[(size_t)t * ldy + c] = from_f32<T>((acc + d_skip * in) * silu_f(gate));
+        }
+    }
+    if (live) {
+#pragma unroll
+        for (int k = 0; k < SPL; ++k) {
+            const int n = lane + lanes * k;
+            if (n < states) S[n] = s[k];
+        }
+    }
+}
+
+template <typename T, int SPL>
+void launch_scan(cudaStream_t stream, const void* u, long long ldu, const float* dt, const float* low, long long ldl, int b_col, int c_col, const float* A,
+                 const float* D, const void* z, long long ldz, float* state, long long slot_floats, long long state_offset, const int* seq_starts,
+                 const int* seq_slots, void* y, long long ldy, int num_seqs, int channels, int states, int lanes) {
+    const int per_block = 128 / lanes;
+    dim3 grid((channels + per_block - 1) / per_block, num_seqs);
+    selective_scan_kernel<T, SPL><<<grid, 128, 0, stream>>>((const T*)u, ldu, dt, low, ldl, b_col, c_col, A, D, (const T*)z, ldz, state, slot_floats,
+                                                           state_offset, seq_starts, seq_slots, (T*)y, ldy, channels, states, lanes);
+}
+
+}  // namespace
+
+// u[t, c] = silu(conv(x)) for every token of the batch, reading what lies before an entry from the request's slot.
+// The slots are not changed: eg_conv_state does that afterwards.
+EG_API int eg_conv_silu(cudaStream_t stream, int dtype, const void* x, long long ldx, const float* conv_w, const float* conv_b, const float* state,
+                        long long slot_floats, const int* token_seq, const int* seq_starts, const int* seq_slots, void* u, long long ldu, int tokens,
+                        int channels, int taps) {
+    const long long n = (long long)tokens * channels;
+    if (n <= 0) return 0;
+    if (taps < 1) return (int)cudaErrorInvalidValue;
+    const unsigned blocks = (unsigned)((n + 255) / 256);
+    if (dtype == EG_BF16)
+        conv_silu_kernel<bf16><<<blocks, 256, 0, stream>>>((const bf16*)x, ldx, conv_w, conv_b, state, slot_floats, token_seq, seq_starts, seq_slots, (bf16*)u,
+                                                          ldu, tokens, channels, taps);
+    else
+        conv_silu_kernel<float><<<blocks, 256, 0, stream>>>((const float*)x, ldx, conv_w, conv_b, state, slot_floats, token_seq, seq_starts, seq_slots,
+                                                           (float*)u, ldu, tokens, channels, taps);
+    return eg_launch_status();
+}
+
+// the slots' convolution rows after this step's tokens
+EG_API int eg_conv_state(cudaStream_t stream, int dtype, const void* x, long long ldx, float* state, long long slot_floats, const int* seq_starts,
+                         const int* seq_slots, int num_seqs, int channels, int taps) {
+    const long long n = (long long)num_seqs * channels;
+    if (n <= 0 || taps <= 1) return 0;
+    const unsigned blocks = (unsigned)((n + 255) / 256);
+    if (dtype == EG_BF16) conv_state_kernel<bf16><<<blocks, 256, 0, stream>>>((const bf16*)x, ldx, state, slot_floats, seq_starts, seq_slots, num_seqs, channels, taps);
+    else conv_state_kernel<float><<<blocks, 256, 0, stream>>>((const float*)x, ldx, state, slot_floats, seq_starts, seq_slots, num_seqs, channels, taps);
+    return eg_launch_status();
+}
+
+// dt [tokens, channels] float32 = softplus(low[:, :rank] dw^T + db)
+EG_API int eg_step_sizes(cudaStream_t stream, const float* low, long long ldl, const float* dw, const float* db, float* dt, int tokens, int channels,
+                         int rank) {
+    const long long n = (long long)tokens * channels;
+    if (n <= 0) return 0;
+    step_size_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(low, ldl, dw, db, dt, tokens, channels, rank);
+    return eg_launch_status();
+}
+
+// The recurrence over every entry's tokens, from and back into the slots' states, and the gated output y.
+// states_per_lane: 1, 2, 4, 8, 16 or 32 (how many states a thread keeps; fewer means more threads per channel).
+EG_API int eg_selective_scan(cudaStream_t stream, int dtype, const void* u, long long ldu, const float* dt, const float* low, long long ldl, int b_col,
+                             int c_col, const float* A, const float* D, const void* z, long long ldz, float* state, long long slot_floats,
+                             long long state_offset, const int* seq_starts, const int* seq_slots, void* y, long long ldy, int num_seqs, int channels,
+                             int states, int states_per_lane) {
+    if (num_seqs <= 0 || channels <= 0) return 0;
+    if (states <= 0 || states > 1024) return (int)cudaErrorInvalidValue;
+    int spl = states_per_lane;
+    while ((states + spl - 1) / spl > 32) spl *= 2;
+    if (spl > 32) return (int)cudaErrorInvalidValue;
+    int lanes = 1;
+    while (lanes * spl < states) lanes <<= 1;
+#define EG_SCAN(T, S) \
+    launch_scan<T, S>(stream, u, ldu, dt, low, ldl, b_col, c_col, A, D, z, ldz, state, slot_floats, state_offset, seq_starts, seq_slots, y, ldy, num_seqs, \
+                      channels, states, lanes)
+#define EG_SCAN_T(T)                      \
+    switch (spl) {                        \
+        case 1: EG_SCAN(T, 1); break;     \
+        case 2: EG_SCAN(T, 2); break;     \
+        case 4: EG_SCAN(T, 4); break;     \
+        case 8: EG_SCAN(T, 8); break;     \
+        case 16: EG_SCAN(T, 16); break;   \
+        case 32: EG_SCAN(T, 32); break;   \
+        default: return (int)cudaErrorInvalidValue; \
+    }
+    if (dtype == EG_BF16) { EG_SCAN_T(bf16) } else { EG_SCAN_T(float) }
+#undef EG_SCAN_T
+#undef EG_SCAN
+    return eg_launch_status();
+}
