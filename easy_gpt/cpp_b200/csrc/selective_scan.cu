@@ -20,6 +20,31 @@ namespace {
 __device__ __forceinline__ float silu_f(float v) { return v / (1.0f + expf(-v)); }
 __device__ __forceinline__ float softplus_f(float v) { return v > 20.0f ? v : log1pf(expf(v)); }
 
+// exp(a * b) for a * b <= 0, rounded to nearest in all but rare cases.  A state that decays slowly is multiplied by
+// thousands of such factors in a row, so an error with a sign of its own (the hardware's 2^x approximation behind expf
+// has one) adds up over a long sequence where errors of either sign would not: measured on a sequence of 1,100 tokens,
+// the logits were 4e-5 of their spread away from a float64 computation with expf and 1e-5 with this.  The product's rounding error is carried into
+// the reduced argument; e^r on |r| <= ln2 / 2 is 1 + r + r^2 P(r) with the last addition the only rounding that counts.
+__device__ __forceinline__ float decay_factor(float a, float b) {
+    const float x = a * b;
+    const float x_lo = fmaf(a, b, -x);
+    if (x < -104.0f) return 0.0f;
+    const float k = rintf(x * 1.442695041f);
+    float r = fmaf(k, -0.693145751953125f, x);          // ln 2 in two pieces: the first has few enough bits for k * it to be exact
+    r = fmaf(k, -1.428606765330187e-06f, r);
+    r += x_lo;
+    float p = 1.9875691500e-4f;
+    p = fmaf(p, r, 1.3981999507e-3f);
+    p = fmaf(p, r, 8.3334519073e-3f);
+    p = fmaf(p, r, 4.1665795894e-2f);
+    p = fmaf(p, r, 1.6666665459e-1f);
+    p = fmaf(p, r, 5.0000001201e-1f);
+    const float e = 1.0f + fmaf(r * r, p, r);
+    const int ki = (int)k;                              // 2^k by exponent arithmetic; results below the normal range go through two steps
+    if (ki >= -125) return __int_as_float(__float_as_int(e) + (ki << 23));
+    return __int_as_float(__float_as_int(e) + ((ki + 100) << 23)) * 7.888609052210118e-31f;      // 2^-100
+}
+
 // one thread per (token, channel)
 template <typename T>
 __global__ void conv_silu_kernel(const T* __restrict__ x, long long ldx, const float* __restrict__ cw, const float* __restrict__ cb,
@@ -103,7 +128,7 @@ __global__ void __launch_bounds__(128) selective_scan_kernel(const T* __restrict
         for (int k = 0; k < SPL; ++k) {
             const int n = lane + lanes * k;
             if (n < states) {
-                s[k] = fmaf(expf(step * a[k]), s[k], drive * Bt[n]);
+                s[k] = fmaf(decay_factor(step, a[k]), s[k], drive * Bt[n]);
                 acc = fmaf(s[k], Ct[n], acc);
             }
         }
