@@ -193,6 +193,70 @@ int main(int argc, char** argv) {
         bad.validate();                                                                                             // a layer twice, a shared cache: fine
     }
 
+
+    // ---- a design whose config.json lists its layers: mixers by type, a repeated run of layers, parallel sub-layers --------------
+    {
+        const char* kListed = R"({"architecture": "Gufanex", "vocab": 97, "width": 40, "norm": {"eps": 1e-5}, "logit_softcap": 12.5,
+          "loop": {"start": 1, "stop": 3, "times": 2},
+          "layers": [
+            {"type": "latent_attention", "mixer": {"heads": 3, "dim": 8, "rot_dim": 4, "vdim": 6, "kv_rank": 20, "q_rank": 24, "scale": 0.3,
+                                                   "rot": {"base": 500.0, "dims": 4}}, "mlp": null},
+            {"type": "mamba1", "mixer": {"inner": 48, "state": 5, "dt_rank": 3, "conv": 3},
+             "mlp": {"kind": "moe", "expert": {"ff": 16}, "router": {"experts": 5, "identity": 2, "top": 2}, "shared": {"ff": 24}}},
+            {"type": "latent_attention", "mixer": {"heads": 1, "dim": 16, "rot_dim": 8, "vdim": 16, "kv_rank": 12, "q_rank": 8, "scale": 0.25,
+                                                   "rot": {"base": 10000.0, "dims": 8}},
+             "mlp": {"kind": "moe", "expert": {"ff": 8}, "router": {"experts": 2, "identity": 0, "top": 1}}},
+            {"type": "mamba1", "mixer": {"inner": 16, "state": 2, "dt_rank": 1, "conv": 2}, "mlp": null}]})";
+        const ModelSpec spec = ArchitectureRegistry::instance().build(json::parse(kListed));
+        CHECK(spec.architecture == "gufanex" && spec.layers.size() == 4 && spec.vocab_size == 97 && spec.hidden_size == 40);
+        // layer 0, then layers 1 and 2 twice with a cache each, then layer 3
+        CHECK(spec.run_order.size() == 6);
+        const int layers[] = {0, 1, 2, 1, 2, 3};
+        for (size_t i = 0; i < spec.run_order.size(); ++i) CHECK(spec.run_order[i].layer == layers[i] && spec.run_order[i].cache == (int)i && spec.run_order[i].writes_cache);
+        // a pass starts with the pass's learned vector; every pass but the first also adds the embedding's output
+        CHECK(spec.stream_adds.size() == 1 && spec.stream_adds[0].prefix == "loop.step" && spec.stream_adds[0].params.integer("rows") == 2);
+        CHECK(spec.run_order[1].stream_add == 0 && spec.run_order[1].stream_add_row == 0 && !spec.run_order[1].add_embedding);
+        CHECK(spec.run_order[3].stream_add == 0 && spec.run_order[3].stream_add_row == 1 && spec.run_order[3].add_embedding);
+        CHECK(spec.run_order[0].stream_add < 0 && spec.run_order[2].stream_add < 0 && spec.run_order[4].stream_add < 0 && spec.run_order[5].stream_add < 0);
+        CHECK(spec.layers[0].parallel && spec.layers[0].sublayers.size() == 1 && spec.layers[1].sublayers.size() == 2);
+        const PartSpec& latent = spec.layers[0].sublayers[0].part;
+        CHECK(latent.kind == "latent_attention" && latent.prefix == "l0.mix" && latent.params.integer("kv_rank") == 20 && latent.params.real("scale") == 0.3 &&
+              latent.params.real("rot_base") == 500.0 && latent.params.integer("rot_dims") == 4 && latent.params.real("eps") == 1e-5);
+        const PartSpec& scan = spec.layers[1].sublayers[0].part;
+        CHECK(scan.kind == "selective_scan" && scan.params.integer("inner") == 48 && scan.params.integer("state") == 5 && scan.params.integer("conv") == 3);
+        const PartSpec& routed = spec.layers[1].sublayers[1].part;
+        CHECK(routed.kind == "routed_experts" && routed.prefix == "l1.mlp" && routed.params.integer("experts") == 5 && routed.params.integer("identity") == 2 &&
+              routed.params.integer("top") == 2 && routed.params.integer("ff") == 16 && routed.params.integer("shared_ff") == 24);
+        CHECK(spec.layers[2].sublayers[1].part.params.integer("shared_ff") == 0);
+        CHECK(spec.layers[1].sublayers[1].norm.kind == "layernorm" && spec.layers[1].sublayers[1].norm.prefix == "l1.norm2" &&
+              spec.layers[1].sublayers[1].norm.params.text("bias_name") == ".b");
+        CHECK(spec.lm_head.params.real("softcap") == 12.5 && spec.embedding.prefix == "embed" && spec.final_norm.prefix == "final.norm");
+        auto listed = [&](const std::string& from, const std::string& to) {
+            std::string text = kListed;
+            const size_t at = text.find(from);
+            if (at == std::string::npos) throw std::logic_error("the test's configuration has no " + from);
+            text.replace(at, from.size(), to);
+            return ArchitectureRegistry::instance().build(json::parse(text));
+        };
+        const std::string loop = "\"loop\": {\"start\": 1, \"stop\": 3, \"times\": 2},";
+        CHECK(listed(loop, "").run_order.size() == 4 && listed(loop, "").stream_adds.empty());          // no loop: every layer once
+        CHECK(listed(loop, "\"loop\": {\"start\": 0, \"stop\": 4, \"times\": 3},").run_order.size() == 12);
+        CHECK(listed(loop, "\"loop\": {\"start\": 2, \"stop\": 2, \"times\": 3},").run_order.size() == 4);    // an empty run of layers
+        CHECK(!listed("\"logit_softcap\": 12.5,", "").lm_head.params.has("softcap"));
+        CHECK(throws<ConfigError>([&] { listed(loop, "\"loop\": {\"start\": 2, \"stop\": 5, \"times\": 2},"); }, "loop must have"));
+        CHECK(throws<ConfigError>([&] { listed("\"width\": 40,", ""); }, "config.json lacks width"));
+        CHECK(throws<ConfigError>([&] { listed("{\"eps\": 1e-5}", "{}"); }, "config.json lacks norm.eps"));
+        CHECK(throws<ConfigError>([&] { listed("\"inner\": 48", "\"inner\": \"48\""); }, "layers[1].mixer.inner must be an integer"));
+        CHECK(throws<ConfigError>([&] { listed("\"type\": \"mamba1\"", "\"type\": \"lstm\""); }, "is no mixer of this design"));
+        // a parallel layer's sub-layers all have their norm in front
+        ModelSpec bad = spec;
+        bad.layers[1].sublayers[1].norm_placement = "post";
+        CHECK(throws<std::invalid_argument>([&] { bad.validate(); }, "a parallel layer's sub-layers"));
+        bad = spec;
+        bad.run_order[2].stream_add = 3;
+        CHECK(throws<std::invalid_argument>([&] { bad.validate(); }, "names stream addition 3"));
+    }
+
     if (failures) {
         std::printf("%d checks failed\n", failures);
         return 1;
