@@ -28,6 +28,11 @@ no flush is needed between steps.
 For profiling and for further sizes (one short line each, never the JSON line above):
 
     python bench.py --only decode|prefill|timeline|gemm|attention|serve [--batch B] [--layers L] [--context C] [--sizes 0.5b|1.5b|7b]
+    python bench.py --only gufanex [--batch B] [--context C] [--steps K] [--sizes small|medium]
+
+`gufanex` measures the Gufanex decoder (selective-scan and latent-attention layers with routed experts) at layer sizes
+of real models of those kinds, with random weights, beside a Qwen2 decoder of the same width, depth and active
+feed-forward size: one prompt of 2,048 tokens as one step, and decode steps of a batch at a context.
 
 `serve` runs 64 concurrent requests (prompts of 128..4096 tokens in portions of 512 beside
 decoding requests, 512 new tokens each) through the engine and reports wall-clock tokens a second.
@@ -64,6 +69,25 @@ SIZES = {
     "7b": {"num_hidden_layers": 28, "hidden_size": 3584, "num_attention_heads": 28, "num_key_value_heads": 4,
            "intermediate_size": 18944, "vocab_size": 152064, "tie_word_embeddings": False},
 }
+# Layer sizes for `--only gufanex`: a selective-scan mixer of a 1.4B state-space model's sizes, latent attention and
+# routed experts of a 16B mixture model's sizes ("medium"), and a quarter of that ("small").  Four layers, the middle two
+# passed twice: six layer runs.  QWEN_EQUAL is the dense decoder it is put beside: same width and number of layer runs,
+# as many attention heads of the same size, and a feed-forward as wide as the experts a token uses.
+def gufanex_bench_configs(size):
+    k = {"medium": 1, "small": 2}[size]
+    width, ff, top, experts = 2048 // k, 1408 // k - (1408 // k) % 64, 6, 64 // k
+    scan = {"type": "mamba1", "mixer": {"inner": 2 * width, "state": 16, "dt_rank": width // 16, "conv": 4}}
+    latent = {"type": "latent_attention", "mixer": {"heads": 16 // k, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": 512, "q_rank": 1536 // k,
+                                                    "scale": 192 ** -0.5, "rot": {"base": 10000.0, "dims": 64}}}
+    mlp = {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": experts, "identity": 2, "top": top}, "shared": {"ff": 2 * ff}}
+    gufanex = {"architecture": "Gufanex", "vocab": 32000, "width": width, "norm": {"eps": 1e-6}, "logit_softcap": 30.0,
+               "loop": {"start": 1, "stop": 3, "times": 2},
+               "layers": [dict(scan, mlp=mlp), dict(latent, mlp=mlp), dict(scan, mlp=mlp), dict(latent, mlp=mlp)]}
+    qwen = dict(CONFIG_05B, num_hidden_layers=6, hidden_size=width, num_attention_heads=16 // k, num_key_value_heads=16 // k, head_dim=128,
+                intermediate_size=(top + 2) * ff, vocab_size=32000, tie_word_embeddings=False)
+    return gufanex, qwen
+
+
 CONTEXT = 4096
 PREFILL_TOKENS = 2048
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
@@ -240,6 +264,53 @@ def measure_prefill(folder, config, repeats=5):
             times.append(runner.last_step_device_seconds)
     del runner
     return median(times)
+
+
+def gufanex_folder(config, seed=0):
+    import hashlib
+
+    from easy_gpt.cpp_b200.weights.gufanex_init import write_random_model
+
+    tag = hashlib.sha256(json.dumps(config, sort_keys=True).encode()).hexdigest()[:12]
+    folder = Path(tempfile.gettempdir()) / f"easy_gpt_bench_{os.getuid()}_{tag}_{seed}"
+    if not (folder / "done").is_file():
+        t0 = time.time()
+        write_random_model(folder, config, seed)
+        (folder / "done").write_text("ok")
+        print(f"[bench] wrote random weights to {folder} in {time.time() - t0:.1f}s", file=sys.stderr, flush=True)
+    return folder
+
+
+def measure_prefill_and_decode(folder, vocab, batch, context, steps, warmup):
+    """Through the step function: a prompt of PREFILL_TOKENS tokens as one step (median of five), then `batch` requests
+    brought to `context - steps - warmup` tokens and decoded together; times are the steps' own, on the device."""
+    from easy_gpt.cpp_b200.native import NativeStepRunner
+
+    start = context - steps - warmup
+    pages = (PREFILL_TOKENS + batch * (context + 64)) // 64 + batch + 2
+    runner = NativeStepRunner(folder, "bfloat16", page_size=64, num_pages=pages, max_slots=batch + 1, max_tokens_per_request=max(context, PREFILL_TOKENS) + 64)
+    prompt = prompts_for(1, PREFILL_TOKENS, vocab, seed=99)[0]
+    times = []
+    for i in range(7):
+        runner.run([("p", prompt, [PREFILL_TOKENS - 1])])
+        runner.end("p")
+        if i >= 2:
+            times.append(runner.last_step_device_seconds)
+    out = {"prefill_ms": round(1e3 * median(times), 3), "prefill_tok_s": round(PREFILL_TOKENS / median(times), 1)}
+    prompts = prompts_for(batch, start, vocab, seed=batch)
+    for i, p in enumerate(prompts):
+        for at in range(0, start, 2048):
+            runner.run([(i, p[at:at + 2048], [])])
+    token = [1] * batch
+    times = []
+    for s in range(warmup + steps):
+        logits = runner.run([(i, [token[i]], [0]) for i in range(batch)])
+        token = [int(t) for t in logits.argmax(axis=1)]
+        if s >= warmup:
+            times.append(runner.last_step_device_seconds)
+    out.update(decode_ms_per_step=round(1e3 * median(times), 4), decode_tok_s=round(batch / median(times), 1), decode_graph_replays=runner.info("graph_replays"))
+    del runner
+    return out
 
 
 def print_timeline(folder, config, batch):
@@ -495,7 +566,25 @@ def measure_serving(folder, config, requests=64, new_tokens=512, chunk=512, budg
     return out
 
 
+def run_gufanex(args):
+    size = args.sizes if args.sizes in ("small", "medium") else "medium"
+    gufanex, qwen = gufanex_bench_configs(size)
+    context = min(args.context, 2048) if args.context == CONTEXT else args.context
+    out = {"only": "gufanex", "sizes": size, "batch": args.batch, "context": context, "prefill_tokens": PREFILL_TOKENS, "dtype": "bfloat16",
+           "data": "synthetic (random weights)"}
+    with ClockSampler() as clocks:
+        if args.model in ("both", "gufanex"):
+            out["gufanex"] = measure_prefill_and_decode(gufanex_folder(gufanex), gufanex["vocab"], args.batch, context, args.steps, args.warmup)
+        if args.model in ("both", "qwen2"):
+            out["qwen2_equal"] = measure_prefill_and_decode(model_folder(qwen), qwen["vocab_size"], args.batch, context, args.steps, args.warmup)
+    out["clocks"] = clocks.summary()
+    print(json.dumps(out))
+    return 0
+
+
 def run_ours(args):
+    if args.only == "gufanex":
+        return run_gufanex(args)
     config = dict(CONFIG_05B, **SIZES[args.sizes])
     if args.sizes != "0.5b" and not args.only:
         print("bench.py: --sizes other than 0.5b goes with --only (the JSON line is defined for the 0.5B sizes)")
@@ -623,14 +712,15 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration (named in config)")
     ap.add_argument("--context", type=int, default=CONTEXT, help="context length the decode steps end at (default 4096)")
-    ap.add_argument("--sizes", choices=list(SIZES), default="0.5b", help="layer sizes for --only runs")
+    ap.add_argument("--sizes", choices=list(SIZES) + ["small", "medium"], default="0.5b", help="layer sizes for --only runs (small, medium: --only gufanex)")
+    ap.add_argument("--model", choices=["both", "gufanex", "qwen2"], default="both", help="with --only gufanex: which of the two models to measure")
     ap.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16", help="precision of --only decode")
     ap.add_argument("--default-options", action="store_true",
                     help="--only decode with the engine's default page size and request length")
     ap.add_argument("--ref-prompt", type=int, default=0,
                     help="prompt length of the reference arm (0: 1536, or the longest its int-indexed logits allow)")
     ap.add_argument("--fused", action="store_true", help="with --only timeline or decode: the decode step as one persistent kernel (EASY_GPT_FUSED_DECODE=1)")
-    ap.add_argument("--only", choices=["decode", "prefill", "timeline", "gemm", "attention", "serve"], default=None,
+    ap.add_argument("--only", choices=["decode", "prefill", "timeline", "gemm", "attention", "serve", "gufanex"], default=None,
                     help="measure one part only and print a short line (for profiling runs)")
     args = ap.parse_args()
     if args.gpus != 1:
