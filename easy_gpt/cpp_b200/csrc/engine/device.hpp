@@ -182,6 +182,19 @@ public:
         if (st != CUBLAS_STATUS_SUCCESS) throw DeviceError("cublasLtMatmul failed with status " + std::to_string((int)st));
     }
 
+    // `batch` products C_i = alpha * op(A_i) B_i in the library's column-major terms (C_i is m x n, op(A_i) m x k, B_i k x n),
+    // bfloat16 operands a fixed stride apart, C bfloat16 or float32.  For per-head maps of an attention whose heads lie
+    // side by side in a row: a head is a stride, not a copy.
+    void gemm_bf16_batched(cudaStream_t stream, bool transpose_a, int m, int n, int k, float alpha, const void* A, long long lda, long long stride_a,
+                           const void* B, long long ldb, long long stride_b, void* C, long long ldc, long long stride_c, bool c_f32, int batch) {
+        const float zero = 0.0f;
+        cublasSetStream(handle_, stream);
+        const cublasStatus_t st = cublasGemmStridedBatchedEx(handle_, transpose_a ? CUBLAS_OP_T : CUBLAS_OP_N, CUBLAS_OP_N, m, n, k, &alpha, A, CUDA_R_16BF, (int)lda,
+                                                             stride_a, B, CUDA_R_16BF, (int)ldb, stride_b, &zero, C, c_f32 ? CUDA_R_32F : CUDA_R_16BF, (int)ldc,
+                                                             stride_c, batch, CUBLAS_COMPUTE_32F, CUBLAS_GEMM_DEFAULT);
+        if (st != CUBLAS_STATUS_SUCCESS) throw DeviceError("cublasGemmStridedBatchedEx failed with status " + std::to_string((int)st));
+    }
+
 private:
     static constexpr size_t kWorkspace = 64u << 20;
     struct Plan {

@@ -96,7 +96,7 @@ int eg_conv_state(cudaStream_t stream, int dtype, const void* x, long long ldx, 
 // selective_scan.cu
 int eg_step_sizes(cudaStream_t stream, const float* low, long long ldl, const float* dw, const float* db, float* dt, int tokens, int channels, int rank);
 // selective_scan.cu
-int eg_selective_scan(cudaStream_t stream, int dtype, const void* u, long long ldu, const float* dt, const float* low, long long ldl, int b_col, int c_col, const float* A, const float* D, const void* z, long long ldz, float* state, long long slot_floats, long long state_offset, const int* seq_starts, const int* seq_slots, void* y, long long ldy, int num_seqs, int channels, int states, int states_per_lane);
+int eg_selective_scan(cudaStream_t stream, int dtype, const void* u, long long ldu, const float* dt, const float* dt_bias, const float* low, long long ldl, int b_col, int c_col, const float* A, const float* D, const void* z, long long ldz, float* state, long long slot_floats, long long state_offset, const int* seq_starts, const int* seq_slots, void* y, long long ldy, int num_seqs, int channels, int states, int states_per_lane);
 // attention_latent.cu
 int eg_latent_prepare(cudaStream_t stream, const float* down, long long ld, int q_rank, int rank, int rot, int rot_dims, const float* gain_q, const float* gain_c, float eps, const float* inv_freq, const int* positions, const int* slot_map, void* cache, int cache_dtype, int page_size, long long page_stride, long long pool_slots, void* cq, int cq_dtype, int tokens, int* status);
 // attention_latent.cu
@@ -111,4 +111,18 @@ int eg_moe_route(cudaStream_t stream, int dtype, const void* h, long long ld, co
 int eg_moe_hidden(cudaStream_t stream, int dtype, const void* h, long long ld, const void* gate_up, const int* ids, void* act, int tokens, int width, int ff, int top, int experts);
 // moe.cu
 int eg_moe_combine(cudaStream_t stream, int dtype, const void* h, long long ld, const void* act, const void* down, const int* ids, const float* weights, const void* shared, int shared_dtype, const float* gate, float* out, int tokens, int width, int ff, int top, int experts);
+// moe.cu
+int eg_moe_dispatch(cudaStream_t stream, const void* h, long long ld, const int* ids, int* counts, int* starts, int* cursors, int* tile_group, int* row_of, void* rows, int tokens, int width, int top, int experts, int max_rows);
+// moe.cu
+int eg_moe_gather(cudaStream_t stream, const void* y, const int* row_of, const int* ids, const float* weights, const void* h, long long ld, const void* shared, int shared_dtype, const float* gate, float* out, int tokens, int width, int top, int experts);
+// gemm_tcgen05.cu
+int eg_gemm_tcgen05_grouped(cudaStream_t stream, int epilogue, const void* A, long long lda, const void* W, long long ldw, void* out, long long ldo, int max_rows, int N, int K, int groups, const int* tile_group, int* status);
+// gemm_tcgen05.cu
+int eg_gemm_tcgen05_few(cudaStream_t stream, int epilogue, int use_pdl, const void* A, long long lda, const void* W, long long ldw, const float* bias, void* out, long long ldo, int M, int N, int K, int tile_n, int slices, float* partial, int* tickets, int* status);
+// attention_latent_mma.cu
+int eg_attention_latent_mma_takes(int rank, int rot);
+// attention_latent_mma.cu
+int eg_attention_latent_mma(cudaStream_t stream, const void* qa, const void* cache, const int* block_table, int table_stride, const int* token_seq, const int* positions, const float* sink, void* out, float* part_o, float* part_ml, int tokens, int heads, int rank, int rot, int page_size, long long page_stride, int num_pages, int splits, int* status);
+// attention_latent_mma.cu
+int eg_latent_rotate_query(cudaStream_t stream, const void* q, long long ldq, const int* positions, const float* inv_freq, int rot_dims, float scale, void* qa, int tokens, int heads, int dim, int rot, int rank);
 }  // extern "C"

@@ -35,6 +35,15 @@ public:
         in_ = Linear(need_tensor(file, prefix + ".in"), nullptr, dtype);
         x_ = Linear(need_tensor(file, prefix + ".x"), nullptr, dtype);
         out_ = Linear(need_tensor(file, prefix + ".o"), nullptr, dtype);
+        // bfloat16 with a rank the products take: the step sizes' projection is a product of its own on the tensor cores
+        // (then the rows of W_x for it and those for B and C are two products, one with bfloat16 output to feed it)
+        split_ = dtype == DType::BF16 && rank_ % 8 == 0;
+        if (split_) {
+            const std::vector<float> wx = host_floats(need_tensor(file, prefix + ".x"));
+            x_dt_ = Linear(wx.data(), rank_, inner_, nullptr, dtype);
+            x_bc_ = Linear(wx.data() + (size_t)rank_ * inner_, 2 * states_, inner_, nullptr, dtype);
+            dt_ = Linear(need_tensor(file, prefix + ".dt"), nullptr, dtype);
+        }
         auto f32 = [&](const std::string& name) {
             const std::vector<float> v = host_floats(need_tensor(file, prefix + name));
             return upload(v.data(), v.size(), DType::F32);
@@ -51,7 +60,7 @@ public:
     size_t weight_bytes() const override {
         return in_.weight_bytes() + x_.weight_bytes() + out_.weight_bytes() + (size_t)inner_ * (taps_ + rank_ + states_ + 3) * 4;
     }
-    size_t arena_bytes(long long T) const override { return (size_t)T * ((size_t)4 * inner_ * 4 + (size_t)(rank_ + 2 * states_) * 4 + (size_t)hidden_ * 4) + (1u << 16); }
+    size_t arena_bytes(long long T) const override { return (size_t)T * ((size_t)4 * inner_ * 4 + (size_t)(rank_ + 2 * states_) * 8 + (size_t)hidden_ * 4) + (1u << 16); }
     bool capturable() const override { return true; }
     CacheNeed cache_need() const override { return CacheNeed::state({slot_floats()}); }
     long long slot_floats() const { return (long long)(taps_ - 1) * inner_ + (long long)inner_ * states_; }
@@ -69,11 +78,23 @@ public:
         launch_check(eg_conv_silu(ctx.stream, (int)dtype, xz.p, xz.ld, conv_w_.as<float>(), conv_b_.as<float>(), state, slot, ctx.token_seq, ctx.seq_starts,
                                   ctx.seq_slots, u.p, u.ld, T, inner_, taps_), "conv_silu");
         launch_check(eg_conv_state(ctx.stream, (int)dtype, xz.p, xz.ld, state, slot, ctx.seq_starts, ctx.seq_slots, ctx.num_seqs, inner_, taps_), "conv_state");
-        const Rows low = x_(ctx, u, /*out_f32=*/true);                               // [T, R + 2N] float32: low_dt | B | C
-        float* dt = ctx.take<float>((size_t)T * inner_);
-        launch_check(eg_step_sizes(ctx.stream, (const float*)low.p, low.ld, dt_w_.as<float>(), dt_b_.as<float>(), dt, T, inner_, rank_), "step_sizes");
+        Rows low;
+        const float *dt = nullptr, *dt_bias = nullptr;
+        int b_col = rank_;
+        if (split_) {
+            const Rows low_dt = x_dt_(ctx, u);                                       // [T, R] bfloat16
+            low = x_bc_(ctx, u, /*out_f32=*/true);                                   // [T, 2N] float32: B | C
+            dt = (const float*)dt_(ctx, low_dt, /*out_f32=*/true).p;                 // [T, I] float32, before bias and softplus
+            dt_bias = dt_b_.as<float>();
+            b_col = 0;
+        } else {
+            low = x_(ctx, u, /*out_f32=*/true);                                      // [T, R + 2N] float32: low_dt | B | C
+            float* sizes = ctx.take<float>((size_t)T * inner_);
+            launch_check(eg_step_sizes(ctx.stream, (const float*)low.p, low.ld, dt_w_.as<float>(), dt_b_.as<float>(), sizes, T, inner_, rank_), "step_sizes");
+            dt = sizes;
+        }
         Rows y{ctx.take_rows(T, inner_, dtype), dtype, T, inner_, inner_};
-        launch_check(eg_selective_scan(ctx.stream, (int)dtype, u.p, u.ld, dt, (const float*)low.p, low.ld, rank_, rank_ + states_, decay_.as<float>(),
+        launch_check(eg_selective_scan(ctx.stream, (int)dtype, u.p, u.ld, dt, dt_bias, (const float*)low.p, low.ld, b_col, b_col + states_, decay_.as<float>(),
                                        skip_.as<float>(), (const char*)xz.p + (size_t)inner_ * es, xz.ld, state, slot, (long long)(taps_ - 1) * inner_,
                                        ctx.seq_starts, ctx.seq_slots, y.p, y.ld, ctx.num_seqs, inner_, states_,
                                        plans::scan_states_per_lane(inner_, states_)), "selective_scan");
@@ -86,7 +107,8 @@ public:
 
 private:
     int hidden_, inner_, states_, rank_, taps_;
-    Linear in_, x_, out_;
+    Linear in_, x_, out_, x_dt_, x_bc_, dt_;
+    bool split_ = false;
     DeviceBuffer conv_w_, conv_b_, dt_w_, dt_b_, decay_, skip_;
 };
 
@@ -150,7 +172,9 @@ public:
     size_t arena_bytes(long long T) const override {
         const size_t per_token = (size_t)(q_rank_ + rank_ + rot_) * 4 + (size_t)q_rank_ * 4 + (size_t)heads_ * (dim_ + rot_) * 4 + (size_t)heads_ * (rank_ + rot_) * 4 +
                                  (size_t)heads_ * rank_ * 4 + (size_t)heads_ * vdim_ * 4 + (size_t)hidden_ * 4;
-        return (size_t)T * per_token + (1u << 16);
+        // the parts of an attention whose keys are cut: at most two CTAs an SM's worth of them beyond one per token
+        const size_t parts = (size_t)(4 * plans::sm_count() + 64) * 16 * (size_t)(rank_ + 2) * 4;
+        return (size_t)T * per_token + parts + (1u << 16);
     }
     bool capturable() const override { return true; }
     CacheNeed cache_need() const override { return CacheNeed::paged_rows(rank_ + rot_, -1); }
@@ -166,6 +190,35 @@ public:
         launch_check(eg_latent_prepare(ctx.stream, (const float*)down.p, down.ld, q_rank_, rank_, rot_, rot_dims_, gain_q_.as<float>(), gain_c_.as<float>(), eps_,
                                        inv_freq_.as<float>(), ctx.positions, tables.slot_map, cache.writes ? cache.k : nullptr, (int)dtype, cache.page_size,
                                        cache.page_stride, (long long)cache.num_pages * cache.page_size, cq.p, (int)dtype, T, ctx.status), "latent_prepare");
+        const int D = rank_ + rot_;
+        if (dtype == DType::BF16 && eg_attention_latent_mma_takes(rank_, rot_) && (dim_ + rot_) % 8 == 0 && dim_ % 8 == 0 && vdim_ % 8 == 0 && dim_ > 0) {
+            // bfloat16 on the tensor cores: the per-head maps are strided batches of the library's product (a head is a
+            // stride in the row, not a copy), the attention takes the heads of a token as the rows of its products
+            const Rows q = up_q_(ctx, cq);
+            void* qa = ctx.take_rows((size_t)T * heads_, D, dtype);
+            ctx.blas->gemm_bf16_batched(ctx.stream, false, rank_, T, dim_, scale_, up_k_.get(), rank_, (long long)dim_ * rank_, q.p, q.ld, dim_ + rot_, qa,
+                                        (long long)heads_ * D, D, false, heads_);
+            launch_check(eg_latent_rotate_query(ctx.stream, q.p, q.ld, ctx.positions, inv_freq_.as<float>(), rot_dims_, scale_, qa, T, heads_, dim_, rot_, rank_),
+                         "latent_rotate_query");
+            const int splits = plans::latent_attention_splits(T, heads_, ctx.max_context_len);
+            float *part_o = nullptr, *part_ml = nullptr;
+            if (splits > 1) {
+                part_o = ctx.take<float>((size_t)T * heads_ * splits * rank_);
+                part_ml = ctx.take<float>((size_t)T * heads_ * splits * 2);
+            }
+            void* o = ctx.take_rows((size_t)T * heads_, rank_, dtype);
+            launch_check(eg_attention_latent_mma(ctx.stream, qa, cache.k, tables.block_table, tables.table_width, ctx.token_seq, ctx.positions,
+                                                 sink_ ? sinks_.as<float>() : nullptr, o, part_o, part_ml, T, heads_, rank_, rot_, cache.page_size, cache.page_stride,
+                                                 cache.num_pages, splits, ctx.status), "attention_latent_mma");
+            Rows values{ctx.take_rows(T, heads_ * vdim_, dtype), dtype, T, heads_ * vdim_, heads_ * vdim_};
+            ctx.blas->gemm_bf16_batched(ctx.stream, true, vdim_, T, rank_, 1.0f, up_v_.get(), rank_, (long long)vdim_ * rank_, o, (long long)heads_ * rank_, rank_,
+                                        values.p, values.ld, vdim_, false, heads_);
+            const Rows res = out_(ctx, values, /*out_f32=*/true);
+            Delta d;
+            d.p = res.p;
+            d.dtype = res.dtype;
+            return d;
+        }
         const Rows q = up_q_(ctx, cq, /*out_f32=*/true);
         float* qa = ctx.take<float>((size_t)T * heads_ * (rank_ + rot_));
         launch_check(eg_latent_absorb(ctx.stream, (int)dtype, (const float*)q.p, q.ld, up_k_.get(), ctx.positions, inv_freq_.as<float>(), rot_dims_, scale_, qa, T,
@@ -263,8 +316,11 @@ public:
                (shared_ ? shared_->weight_bytes() + (size_t)hidden_ * 4 : 0);
     }
     size_t arena_bytes(long long T) const override {
-        return (size_t)T * ((size_t)top_ * (8 + (size_t)ff_ * 4) + 4 + (size_t)hidden_ * 8 + (size_t)shared_ff_ * 3 * 4) + (1u << 16);
+        const size_t sorted = (size_t)grouped_rows(T) * ((size_t)hidden_ + ff_) * 2 + (size_t)grouped_rows(T) / 32 + (size_t)experts_ * 16;
+        return (size_t)T * ((size_t)top_ * (12 + (size_t)ff_ * 4) + 4 + (size_t)hidden_ * 8 + (size_t)shared_ff_ * 3 * 4) + sorted + (1u << 16);
     }
+    // rows of the sorted copy of a step of T tokens: every expert's run starts at a multiple of 128
+    int grouped_rows(long long T) const { return (int)((T * top_ + 127) / 128 * 128 + 128LL * experts_); }
     bool capturable() const override { return true; }
 
     Delta forward(const StepContext& ctx, PartInput in, const FollowingNorm*) override {
@@ -282,9 +338,30 @@ public:
             rows.rows = h;
             shared = shared_->forward(ctx, rows, nullptr);
         }
+        float* out = ctx.take<float>((size_t)T * hidden_);
+        if (plans::moe_grouped_takes(dtype, T, hidden_, ff_, experts_)) {
+            // many tokens: rows sorted by expert, one grouped product on the tensor cores per projection
+            const int max_rows = grouped_rows(T);
+            int* scratch = ctx.take<int>((size_t)3 * experts_ + 1 + max_rows / 128 + (size_t)T * top_);
+            int *counts = scratch, *starts = counts + experts_, *cursors = starts + experts_ + 1, *tile_group = cursors + experts_,
+                *row_of = tile_group + max_rows / 128;
+            void* rows = ctx.take_rows(max_rows, hidden_, dtype);
+            launch_check(eg_moe_dispatch(ctx.stream, h.p, h.ld, ids, counts, starts, cursors, tile_group, row_of, rows, T, hidden_, top_, experts_, max_rows),
+                         "moe_dispatch");
+            void* hidden = ctx.take_rows(max_rows, ff_, dtype);
+            launch_check(eg_gemm_tcgen05_grouped(ctx.stream, plans::EPI_SWIGLU, rows, hidden_, gate_up_.get(), hidden_, hidden, ff_, max_rows, 2 * ff_, hidden_,
+                                                 experts_, tile_group, ctx.status), "gemm_tcgen05_grouped");
+            launch_check(eg_gemm_tcgen05_grouped(ctx.stream, plans::EPI_STORE, hidden, ff_, down_.get(), ff_, rows, hidden_, max_rows, hidden_, ff_, experts_,
+                                                 tile_group, ctx.status), "gemm_tcgen05_grouped");
+            launch_check(eg_moe_gather(ctx.stream, rows, row_of, ids, weights, h.p, h.ld, shared.p, (int)shared.dtype, gate, out, T, hidden_, top_, experts_),
+                         "moe_gather");
+            Delta d;
+            d.p = out;
+            d.dtype = DType::F32;
+            return d;
+        }
         void* act = ctx.take_rows((size_t)T * top_, std::max(ff_, 1), dtype);
         launch_check(eg_moe_hidden(ctx.stream, (int)dtype, h.p, h.ld, gate_up_.get(), ids, act, T, hidden_, ff_, top_, experts_), "moe_hidden");
-        float* out = ctx.take<float>((size_t)T * hidden_);
         launch_check(eg_moe_combine(ctx.stream, (int)dtype, h.p, h.ld, act, down_.get(), ids, weights, shared.p, (int)shared.dtype, gate, out, T, hidden_, ff_,
                                     top_, experts_), "moe_combine");
         Delta d;

@@ -154,6 +154,24 @@ inline bool gemm_tcgen05_wide_takes(DType dtype, int tokens, int out_features, i
            (long long)((tokens + 127) / 128) * (out_features / 256) >= sm_count();
 }
 
+// Into how many parts the tensor-core latent attention cuts a token's keys: while the step has fewer CTAs than two an
+// SM, and a part keeps a tile of 64 keys at least.  A power of two.
+inline int latent_attention_splits(int tokens, int heads, long long max_context) {
+    const long long base = (long long)tokens * ((heads + 15) / 16);
+    const long long tiles = std::max<long long>(1, (max_context + 63) / 64);
+    int splits = 1;
+    while ((long long)splits * 2 * base <= 2LL * sm_count() && splits * 2 <= tiles && splits < 64) splits *= 2;
+    return splits;
+}
+
+// Routed experts: from how many tokens on a step's rows are sorted by expert for one grouped product per projection on
+// the tensor cores, instead of every token reading its experts' weights itself.  The grouped product takes widths that
+// are multiples of 128 and expert sizes that are multiples of 64.
+constexpr int MOE_GROUPED_MIN_TOKENS = 33;
+inline bool moe_grouped_takes(DType dtype, int tokens, int width, int ff, int experts) {
+    return dtype == DType::BF16 && tokens >= MOE_GROUPED_MIN_TOKENS && experts > 0 && width % 128 == 0 && ff % 64 == 0 && ff > 0;
+}
+
 // How many of a channel's states one thread of the selective scan keeps (1, 2, 4, ... 32): as many as still leave a
 // block of threads for every SM when one request is scanned alone.  It hangs off the mixer's sizes alone, never off the
 // batch, so the order of the sum over a channel's states is the same in every step.

@@ -111,6 +111,9 @@ struct Params {
     int epilogue;
     int* status;
     long long* trace;          // optional (profiling): clock stamps of the first pair's MMA thread, three per step of K
+    // grouped products (single-CTA kernel only): row tile i of A is multiplied by the W of group tile_group[i] (W holds
+    // the groups' [N, K] matrices one after the other); a tile whose entry is negative has no rows and is skipped
+    const int* tile_group;
 };
 
 __global__ void __launch_bounds__(THREADS)
@@ -124,6 +127,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n0 = blockIdx.x * BN, m0 = blockIdx.y * BM;
     const int k_blocks = p.K / BK;
+    int w_row0 = n0;
+    if (p.tile_group) {                                          // the whole CTA leaves before it has set anything up
+        const int group = p.tile_group[blockIdx.y];
+        if (group < 0) return;
+        w_row0 = group * p.N + n0;
+    }
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -151,7 +160,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 mbar_expect_tx(&full_bar[s], STAGE_BYTES);
                 unsigned char* a = ring + s * STAGE_BYTES;
                 tma_load_2d(a, &map_a, &full_bar[s], kb * BK, m0);
-                tma_load_2d(a + TILE_A_BYTES, &map_w, &full_bar[s], kb * BK, n0);
+                tma_load_2d(a + TILE_A_BYTES, &map_w, &full_bar[s], kb * BK, w_row0);
             }
         }
     } else if (warp == 1) {
@@ -956,6 +965,30 @@ EG_API int eg_gemm_tcgen05(cudaStream_t stream, int epilogue, const void* A, lon
         return eg_launch_status();
     }
     dim3 grid(N / BN, (M + BM - 1) / BM);
+    gemm_tcgen05_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(map_a, map_w, p);
+    return eg_launch_status();
+}
+
+// Grouped product for routed experts: A [max_rows, K] holds the rows of group after group, each group's rows starting at
+// a multiple of 128; row tile i (128 rows) belongs to group tile_group[i] (device array of max_rows / 128 entries; negative:
+// an empty tile) and is multiplied by that group's W (W [groups * N, K]).  out [max_rows, N] (or [max_rows, N / 2] with the
+// SwiGLU epilogue on interleaved columns), bfloat16.  One launch whatever the groups' sizes, which only the device knows.
+EG_API int eg_gemm_tcgen05_grouped(cudaStream_t stream, int epilogue, const void* A, long long lda, const void* W, long long ldw, void* out,
+                                   long long ldo, int max_rows, int N, int K, int groups, const int* tile_group, int* status) {
+    if (max_rows <= 0 || N <= 0 || groups <= 0) return 0;
+    if (max_rows % BM || N % BN || K % BK || K <= 0 || lda % 8 || ldw % 8 || ldo % 8 || (uintptr_t)A % 16 || (uintptr_t)W % 16 || (uintptr_t)out % 16 ||
+        (epilogue != EPI_STORE && epilogue != EPI_SWIGLU) || !status || !tile_group)
+        return (int)cudaErrorInvalidValue;
+    CUtensorMap map_a, map_w;
+    if (make_map(&map_a, A, max_rows, K, lda, BM) || make_map(&map_w, W, (long long)groups * N, K, ldw, BN)) return (int)cudaErrorInvalidValue;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    Params p{(bf16*)out, ldo, nullptr, max_rows, N, K, epilogue, status, nullptr, tile_group};
+    dim3 grid(N / BN, max_rows / BM);
     gemm_tcgen05_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(map_a, map_w, p);
     return eg_launch_status();
 }

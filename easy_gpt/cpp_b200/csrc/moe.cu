@@ -10,6 +10,12 @@
 //                                + g[t] * shared[t, :]                   (float32)
 //
 // eg_moe_hidden and eg_moe_combine read each chosen expert's weights per token: the form for steps of few tokens.
+// For steps of many tokens the rows are sorted by expert instead, so that every expert's weights meet all of its rows in
+// one grouped product on the tensor cores (eg_gemm_tcgen05_grouped):
+//   eg_moe_dispatch  counts the rows of every expert, gives each expert a run of rows that starts at a multiple of 128,
+//                    says which expert every tile of 128 rows belongs to, and copies each token's row to its places
+//   eg_moe_gather    out[t, :] = sum_k weight[t, k] * (y[row_of[t, k], :] or h[t, :]) + g[t] * shared[t, :]
+// The sizes of the runs stay on the device: nothing here waits for the host.
 // Products accumulate in float32; the router is float32 throughout.
 #include "common.cuh"
 
@@ -128,7 +134,8 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const T* __restrict__ 
 
 }  // namespace
 
-// ids [T, top] int32 (>= experts... see eg_moe_hidden), weights [T, top] float32, gate [T] float32 (only with gate_w)
+// ids [T, top] int32 (router outputs; those >= the number of experts stand for the identity), weights [T, top] float32,
+// gate [T] float32 (only with gate_w)
 EG_API int eg_moe_route(cudaStream_t stream, int dtype, const void* h, long long ld, const float* router, const float* correction, const float* gate_w,
                         int* ids, float* weights, float* gate, int tokens, int width, int outputs, int top) {
     if (tokens <= 0) return 0;
@@ -165,5 +172,102 @@ EG_API int eg_moe_combine(cudaStream_t stream, int dtype, const void* h, long lo
     else
         moe_combine_kernel<float><<<grid, 256, 0, stream>>>((const float*)h, ld, (const float*)act, (const float*)down, ids, weights, shared, shared_dtype,
                                                            gate, out, width, ff, top, experts);
+    return eg_launch_status();
+}
+
+namespace {
+__global__ void moe_count_kernel(const int* __restrict__ ids, int* __restrict__ counts, int pairs, int experts) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < pairs && ids[i] < experts) atomicAdd(&counts[ids[i]], 1);
+}
+// one block: starts[e] = first row of expert e's run (runs padded to 128 rows), cursors to zero, tiles labelled
+__global__ void moe_offsets_kernel(const int* __restrict__ counts, int* __restrict__ starts, int* __restrict__ cursors, int* __restrict__ tile_group,
+                                   int experts, int max_tiles) {
+    for (int i = threadIdx.x; i < max_tiles; i += blockDim.x) tile_group[i] = -1;
+    if (threadIdx.x == 0) {
+        int at = 0;
+        for (int e = 0; e < experts; ++e) {
+            starts[e] = at;
+            at += (counts[e] + 127) / 128 * 128;
+        }
+        starts[experts] = at;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < experts; e += blockDim.x) {
+        cursors[e] = 0;
+        for (int tile = starts[e] / 128; tile < starts[e + 1] / 128 && tile < max_tiles; ++tile) tile_group[tile] = e;
+    }
+}
+// a warp per (token, choice): takes the next row of the expert's run and copies the token's row there
+__global__ void __launch_bounds__(256) moe_scatter_kernel(const bf16* __restrict__ h, long long ld, const int* __restrict__ ids, const int* __restrict__ starts,
+                                                          int* __restrict__ cursors, int* __restrict__ row_of, bf16* __restrict__ rows, int pairs, int width,
+                                                          int top, int experts, int max_rows) {
+    const int pair = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (pair >= pairs) return;
+    const int e = ids[pair];
+    if (e >= experts) {
+        if (lane == 0) row_of[pair] = -1;
+        return;
+    }
+    int row = 0;
+    if (lane == 0) {
+        row = starts[e] + atomicAdd(&cursors[e], 1);
+        if (row >= max_rows) row = -1;
+        row_of[pair] = row;
+    }
+    row = __shfl_sync(0xffffffffu, row, 0);
+    if (row < 0) return;
+    const bf16* src = h + (size_t)(pair / top) * ld;
+    bf16* dst = rows + (size_t)row * width;
+    if (width % 8 == 0 && ld % 8 == 0) {
+        for (int j = lane; j < width / 8; j += 32) reinterpret_cast<uint4*>(dst)[j] = reinterpret_cast<const uint4*>(src)[j];
+    } else {
+        for (int j = lane; j < width; j += 32) dst[j] = src[j];
+    }
+}
+__global__ void moe_gather_kernel(const bf16* __restrict__ y, const int* __restrict__ row_of, const int* __restrict__ ids, const float* __restrict__ weights,
+                                  const bf16* __restrict__ h, long long ld, const void* __restrict__ shared, int shared_dtype, const float* __restrict__ gate,
+                                  float* __restrict__ out, int tokens, int width, int top, int experts) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long long)tokens * width) return;
+    const int t = (int)(i / width), j = (int)(i % width);
+    float total = 0.f;
+    for (int k = 0; k < top; ++k) {
+        const int e = ids[(size_t)t * top + k];
+        const float wgt = weights[(size_t)t * top + k];
+        if (e >= experts) total += wgt * __bfloat162float(h[(size_t)t * ld + j]);
+        else {
+            const int row = row_of[(size_t)t * top + k];
+            if (row >= 0) total += wgt * __bfloat162float(y[(size_t)row * width + j]);
+        }
+    }
+    if (shared) total += gate[t] * (shared_dtype == EG_BF16 ? __bfloat162float(((const bf16*)shared)[i]) : ((const float*)shared)[i]);
+    out[i] = total;
+}
+}  // namespace
+
+// Sorts the step's (token, choice) pairs by expert (bfloat16 rows).  counts, cursors [experts] and starts [experts + 1] are
+// scratch; tile_group [max_rows / 128] and row_of [tokens * top] are results, rows [max_rows, width] receives the copies.
+// max_rows: a multiple of 128, at least tokens * top rounded up to 128 plus 128 per expert.
+EG_API int eg_moe_dispatch(cudaStream_t stream, const void* h, long long ld, const int* ids, int* counts, int* starts, int* cursors, int* tile_group,
+                           int* row_of, void* rows, int tokens, int width, int top, int experts, int max_rows) {
+    const int pairs = tokens * top;
+    if (pairs <= 0 || experts <= 0) return 0;
+    if (max_rows % 128 || max_rows < (pairs + 127) / 128 * 128 + 128 * experts || experts > 2048) return (int)cudaErrorInvalidValue;
+    cudaError_t e = cudaMemsetAsync(counts, 0, (size_t)experts * sizeof(int), stream);
+    if (e != cudaSuccess) return (int)e;
+    moe_count_kernel<<<(pairs + 255) / 256, 256, 0, stream>>>(ids, counts, pairs, experts);
+    moe_offsets_kernel<<<1, 256, 0, stream>>>(counts, starts, cursors, tile_group, experts, max_rows / 128);
+    moe_scatter_kernel<<<(pairs + 7) / 8, 256, 0, stream>>>((const bf16*)h, ld, ids, starts, cursors, row_of, (bf16*)rows, pairs, width, top, experts, max_rows);
+    return eg_launch_status();
+}
+
+// out [T, width] float32 from the experts' outputs y [max_rows, width] (bfloat16) in sorted order
+EG_API int eg_moe_gather(cudaStream_t stream, const void* y, const int* row_of, const int* ids, const float* weights, const void* h, long long ld,
+                         const void* shared, int shared_dtype, const float* gate, float* out, int tokens, int width, int top, int experts) {
+    const long long n = (long long)tokens * width;
+    if (n <= 0) return 0;
+    moe_gather_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>((const bf16*)y, row_of, ids, weights, (const bf16*)h, ld, shared, shared_dtype, gate, out,
+                                                                      tokens, width, top, experts);
     return eg_launch_status();
 }

@@ -97,8 +97,8 @@ __global__ void step_size_kernel(const float* __restrict__ low, long long ldl, c
 // states is LANES' shuffle steps.  A block covers blockDim.x / LANES channels of one entry.
 template <typename T, int SPL>
 __global__ void __launch_bounds__(128) selective_scan_kernel(const T* __restrict__ u, long long ldu, const float* __restrict__ dt,
-                                                             const float* __restrict__ low, long long ldl, int b_col, int c_col,
-                                                             const float* __restrict__ A, const float* __restrict__ D, const T* __restrict__ z,
+                                                             const float* __restrict__ dt_bias, const float* __restrict__ low, long long ldl, int b_col,
+                                                             int c_col, const float* __restrict__ A, const float* __restrict__ D, const T* __restrict__ z,
                                                              long long ldz, float* __restrict__ state, long long slot_floats, long long state_offset,
                                                              const int* __restrict__ seq_starts, const int* __restrict__ seq_slots, T* __restrict__ y,
                                                              long long ldy, int channels, int states, int lanes) {
@@ -116,9 +116,11 @@ __global__ void __launch_bounds__(128) selective_scan_kernel(const T* __restrict
         a[k] = n < states ? A[(size_t)cc * states + n] : 0.f;
     }
     const float d_skip = D[cc];
+    const float step_bias = dt_bias ? dt_bias[cc] : 0.f;
     const int t0 = seq_starts[seq], t1 = seq_starts[seq + 1];
     for (int t = t0; t < t1; ++t) {
-        const float step = dt[(size_t)t * channels + cc];
+        float step = dt[(size_t)t * channels + cc];
+        if (dt_bias) step = softplus_f(step + step_bias);        // dt holds the projection alone: bias and softplus happen here
         const float in = to_f32<T>(u[(size_t)t * ldu + cc]);
         const float drive = step * in;
         const float* Bt = low + (size_t)t * ldl + b_col;
@@ -148,12 +150,12 @@ __global__ void __launch_bounds__(128) selective_scan_kernel(const T* __restrict
 }
 
 template <typename T, int SPL>
-void launch_scan(cudaStream_t stream, const void* u, long long ldu, const float* dt, const float* low, long long ldl, int b_col, int c_col, const float* A,
+void launch_scan(cudaStream_t stream, const void* u, long long ldu, const float* dt, const float* dt_bias, const float* low, long long ldl, int b_col, int c_col, const float* A,
                  const float* D, const void* z, long long ldz, float* state, long long slot_floats, long long state_offset, const int* seq_starts,
                  const int* seq_slots, void* y, long long ldy, int num_seqs, int channels, int states, int lanes) {
     const int per_block = 128 / lanes;
     dim3 grid((channels + per_block - 1) / per_block, num_seqs);
-    selective_scan_kernel<T, SPL><<<grid, 128, 0, stream>>>((const T*)u, ldu, dt, low, ldl, b_col, c_col, A, D, (const T*)z, ldz, state, slot_floats,
+    selective_scan_kernel<T, SPL><<<grid, 128, 0, stream>>>((const T*)u, ldu, dt, dt_bias, low, ldl, b_col, c_col, A, D, (const T*)z, ldz, state, slot_floats,
                                                            state_offset, seq_starts, seq_slots, (T*)y, ldy, channels, states, lanes);
 }
 
@@ -198,9 +200,11 @@ EG_API int eg_step_sizes(cudaStream_t stream, const float* low, long long ldl, c
 }
 
 // The recurrence over every entry's tokens, from and back into the slots' states, and the gated output y.
+// dt_bias null: dt holds the step sizes.  Otherwise dt holds their projection alone and the step size is
+// softplus(dt + dt_bias[c]) (the projection then came from a matrix product, and this kernel finishes it).
 // states_per_lane: 1, 2, 4, 8, 16 or 32 (how many states a thread keeps; fewer means more threads per channel).
-EG_API int eg_selective_scan(cudaStream_t stream, int dtype, const void* u, long long ldu, const float* dt, const float* low, long long ldl, int b_col,
-                             int c_col, const float* A, const float* D, const void* z, long long ldz, float* state, long long slot_floats,
+EG_API int eg_selective_scan(cudaStream_t stream, int dtype, const void* u, long long ldu, const float* dt, const float* dt_bias, const float* low,
+                             long long ldl, int b_col, int c_col, const float* A, const float* D, const void* z, long long ldz, float* state, long long slot_floats,
                              long long state_offset, const int* seq_starts, const int* seq_slots, void* y, long long ldy, int num_seqs, int channels,
                              int states, int states_per_lane) {
     if (num_seqs <= 0 || channels <= 0) return 0;
@@ -211,7 +215,7 @@ EG_API int eg_selective_scan(cudaStream_t stream, int dtype, const void* u, long
     int lanes = 1;
     while (lanes * spl < states) lanes <<= 1;
 #define EG_SCAN(T, S) \
-    launch_scan<T, S>(stream, u, ldu, dt, low, ldl, b_col, c_col, A, D, z, ldz, state, slot_floats, state_offset, seq_starts, seq_slots, y, ldy, num_seqs, \
+    launch_scan<T, S>(stream, u, ldu, dt, dt_bias, low, ldl, b_col, c_col, A, D, z, ldz, state, slot_floats, state_offset, seq_starts, seq_slots, y, ldy, num_seqs, \
                       channels, states, lanes)
 #define EG_SCAN_T(T)                      \
     switch (spl) {                        \

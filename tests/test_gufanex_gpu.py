@@ -94,6 +94,11 @@ ALONE = {
     "routed": model([(scan(inner=16, state=2, dt_rank=1, conv=2), routed())]),
     "routed_many": model([(scan(inner=16, state=2, dt_rank=1, conv=2), routed(experts=40, identity=5, top=6, ff=16, shared=0))]),
     "loop": model([(scan(inner=32, state=4), None), (latent(), None)], loop=(0, 2, 3)),
+    # more heads than one tile of the tensor-core attention has rows
+    "latent_many_heads": model([(latent(heads=20, dim=8, rot_dim=8, vdim=8, kv_rank=16, q_rank=16, scale=0.25), None)]),
+    # sizes that the grouped product on the tensor cores takes (steps of 33 tokens and more, bfloat16)
+    "routed_grouped": model([(scan(inner=16, state=2, dt_rank=8, conv=2), routed(experts=5, identity=2, top=3, ff=64, shared=64))], width=128),
+    "scan_wide_rank": model([(scan(inner=64, state=16, dt_rank=16, conv=4), None)], width=64),
 }
 
 
