@@ -5,8 +5,9 @@
 // token against a tile of 64 keys is a 16 x 64 x (rank + rot) product, and the weighted sum a 16 x rank x 64 one: shapes
 // that mma.sync m16n8k16 takes as they are, for a prompt's tokens and for single decoded tokens alike.  A CTA of four
 // warps takes (token, group of 16 heads, part of the keys):
-//   the queries qa [16, D] and, tile by tile, 64 cached rows [64, D] go to shared memory (cp.async, zero-filled beyond
-//     the token's position); the cached rows are read once for scores and values;
+//   the queries qa [16, D] and, tile by tile, 64 cached rows [64, D] go to shared memory: one bulk copy (cp.async.bulk,
+//     counted on an mbarrier) per cached row, issued by the lanes of the first warp, rows beyond the token's position
+//     zeroed; the cached rows are read once for scores and values; the wait on the mbarrier is bounded;
 //   scores: warp w computes the tile's keys 16 w .. 16 w + 15 for all 16 heads; row maxima and sums meet in shared memory;
 //   the weights go to shared memory as bfloat16 and every warp adds its share of the value columns (columns 16 (w + 4 i)..)
 //     from the same key tile, read transposed by ldmatrix;
@@ -14,6 +15,7 @@
 //     merges the parts and the sink.
 // Scores, maxima, sums and the accumulators are float32.  Takes D = rank + rot a multiple of 8, rank a multiple of 8 up
 // to 512; anything else: cudaErrorInvalidValue, and the caller uses the generic kernel.
+#include "mbarrier.cuh"
 #include "mma_utils.cuh"
 
 namespace {
@@ -35,6 +37,8 @@ __global__ void __launch_bounds__(WARPS * 32) attention_latent_mma_kernel(const 
                                                                           float* __restrict__ part_ml, int heads, int rank, int rot, int page_size,
                                                                           long long page_stride, int num_pages, int splits, int* __restrict__ status) {
     extern __shared__ __align__(16) unsigned char smem[];
+    __shared__ __align__(8) uint64_t bar;
+    __shared__ int abort_flag;
     const int D = rank + rot, D16 = (D + 15) / 16 * 16, DS = D16 + 8;           // row stride in elements: 16 bytes past a multiple of 32
     bf16* Qs = reinterpret_cast<bf16*>(smem);
     bf16* Ks = Qs + 16 * DS;
@@ -64,26 +68,38 @@ __global__ void __launch_bounds__(WARPS * 32) attention_latent_mma_kernel(const 
             for (int k = 0; k < 4; ++k) o[i][j][k] = 0.f;
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};      // rows lane / 4 and lane / 4 + 8
     const int chunks = D / 8;                                               // 16-byte pieces of a cached row
+    const uint32_t row_bytes = (uint32_t)D * 2;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    __syncthreads();
 
     for (int tile = tile0; tile < tile1; ++tile) {
         const int j0 = tile * KT;
-        for (int i = threadIdx.x; i < KT * chunks; i += blockDim.x) {
-            const int r = i / chunks, c = i % chunks, j = j0 + r;
-            bool valid = j <= last;
-            const bf16* src = cache;
-            if (valid) {
-                const int page = table[j / page_size];
-                if (page < 0 || page >= num_pages) {
+        const int valid_rows = min(KT, last - j0 + 1);
+        if (warp == 0) {
+            // the buffer was last touched by ldmatrix and plain stores: order them before the copies that overwrite it
+            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+            if (lane == 0) mbar_expect_tx(&bar, (uint32_t)valid_rows * row_bytes);
+            __syncwarp();
+            for (int r = lane; r < valid_rows; r += 32) {
+                const int j = j0 + r, page = table[j / page_size];
+                if (page < 0 || page >= num_pages) {             // a complaint, and the row's bytes from a page that exists
                     atomicOr(status, EG_STATUS_BAD_PAGE);
-                    valid = false;
-                } else {
-                    src = cache + (size_t)page * page_stride + (size_t)(j % page_size) * D + c * 8;
                 }
+                const int safe = (page < 0 || page >= num_pages) ? 0 : page;
+                const bf16* src = cache + (size_t)safe * page_stride + (size_t)(j % page_size) * D;
+                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(smem_addr(Ks + r * DS)),
+                             "l"(src), "r"(row_bytes), "r"(smem_addr(&bar))
+                             : "memory");
             }
-            cp_async_16(Ks + r * DS + c * 8, src, valid);
+        } else {
+            for (int i = threadIdx.x - 32; i < (KT - valid_rows) * chunks; i += blockDim.x - 32)      // rows past the token's position: zeros
+                *reinterpret_cast<uint4*>(Ks + (valid_rows + i / chunks) * DS + (i % chunks) * 8) = make_uint4(0u, 0u, 0u, 0u);
         }
-        cp_async_commit();
-        cp_async_wait<0>();
+        if (!mbar_wait_bounded(&bar, (uint32_t)((tile - tile0) & 1), &abort_flag, status, 1u << 24)) break;
         __syncthreads();
 
         // scores of this warp's 16 keys for the 16 heads
@@ -182,6 +198,7 @@ __global__ void __launch_bounds__(WARPS * 32) attention_latent_mma_kernel(const 
         __syncthreads();                                                    // the next tile overwrites the keys and the weights
     }
 
+    if (abort_flag) return;                                                 // a wait gave up: the status word says so, nothing is written
     // a thread holds, per pair of column tiles, rows lane / 4 (values 0, 1) and lane / 4 + 8 (values 2, 3), columns 2 (lane % 4) + {0, 1}
 #pragma unroll
     for (int r = 0; r < 2; ++r) {

@@ -106,7 +106,7 @@ int eg_attention_latent(cudaStream_t stream, int cache_dtype, const float* qa, c
 // attention_latent.cu
 int eg_latent_expand(cudaStream_t stream, int w_dtype, const float* o, const void* Uv, void* out, int out_dtype, long long ldo, int tokens, int heads, int vdim, int rank);
 // moe.cu
-int eg_moe_route(cudaStream_t stream, int dtype, const void* h, long long ld, const float* router, const float* correction, const float* gate_w, int* ids, float* weights, float* gate, int tokens, int width, int outputs, int top);
+int eg_moe_route(cudaStream_t stream, int dtype, const void* h, long long ld, const float* router, const float* correction, const float* gate_w, float* logits, int* ids, float* weights, float* gate, int tokens, int width, int outputs, int top);
 // moe.cu
 int eg_moe_hidden(cudaStream_t stream, int dtype, const void* h, long long ld, const void* gate_up, const int* ids, void* act, int tokens, int width, int ff, int top, int experts);
 // moe.cu

@@ -223,7 +223,7 @@ public:
         : Norm(p, prefix), size_((int)p.integer("size")), eps_((float)p.real("eps")), weight_name_(prefix + p.text("weight_name", ".weight")),
           bias_name_(prefix + p.text("bias_name", ".bias")) {}
     std::vector<TensorRequest> tensor_requests() const override {
-        return {TensorRequest::vector(weight_name_, size_), TensorRequest::vector(bias_name_, size_)};
+        return {TensorRequest::vector(weight_name_, size_).with_init("one"), TensorRequest::vector(bias_name_, size_).with_init("zero")};
     }
     void load(const HostTensors& file, DType) override {
         const std::vector<float> g = host_floats(need_tensor(file, weight_name_)), b = host_floats(need_tensor(file, bias_name_));

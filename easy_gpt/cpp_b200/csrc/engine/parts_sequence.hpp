@@ -22,13 +22,13 @@ public:
         : Mixer(p, prefix, std::move(position)), hidden_((int)p.integer("hidden_size")), inner_((int)p.integer("inner")), states_((int)p.integer("state")),
           rank_((int)p.integer("dt_rank")), taps_((int)p.integer("conv")) {
         if (hidden_ <= 0 || inner_ <= 0 || rank_ <= 0 || taps_ < 1) throw std::invalid_argument("a selective-scan mixer's sizes must be positive");
-        if (states_ <= 0 || states_ > 1024) throw std::invalid_argument("a selective-scan mixer takes 1 to 1024 states per channel");
+        if (states_ <= 0 || states_ > 512) throw std::invalid_argument("a selective-scan mixer takes 1 to 512 states per channel");
     }
     std::vector<TensorRequest> tensor_requests() const override {
         return {TensorRequest::matrix(prefix + ".in", 2LL * inner_, hidden_), TensorRequest::matrix(prefix + ".conv", inner_, taps_),
                 TensorRequest::vector(prefix + ".conv.b", inner_), TensorRequest::matrix(prefix + ".x", rank_ + 2LL * states_, inner_),
-                TensorRequest::matrix(prefix + ".dt", inner_, rank_), TensorRequest::vector(prefix + ".dt.b", inner_),
-                TensorRequest::matrix(prefix + ".A_log", inner_, states_), TensorRequest::vector(prefix + ".D", inner_),
+                TensorRequest::matrix(prefix + ".dt", inner_, rank_), TensorRequest::vector(prefix + ".dt.b", inner_).with_init("step_bias"),
+                TensorRequest::matrix(prefix + ".A_log", inner_, states_).with_init("log_decay"), TensorRequest::vector(prefix + ".D", inner_).with_init("one"),
                 TensorRequest::matrix(prefix + ".o", hidden_, inner_)};
     }
     void load(const HostTensors& file, DType dtype) override {
@@ -137,12 +137,12 @@ public:
         if (rank_ + rot_ > 1024) throw std::invalid_argument("latent attention: kv_rank + rot_dim is beyond what the kernel takes (1024)");
     }
     std::vector<TensorRequest> tensor_requests() const override {
-        std::vector<TensorRequest> r = {TensorRequest::matrix(prefix + ".dq", q_rank_, hidden_), TensorRequest::vector(prefix + ".dq.norm", q_rank_),
+        std::vector<TensorRequest> r = {TensorRequest::matrix(prefix + ".dq", q_rank_, hidden_), TensorRequest::vector(prefix + ".dq.norm", q_rank_).with_init("one"),
                                         TensorRequest::matrix(prefix + ".uq", (long long)heads_ * (dim_ + rot_), q_rank_),
-                                        TensorRequest::matrix(prefix + ".dkv", rank_ + rot_, hidden_), TensorRequest::vector(prefix + ".dkv.norm", rank_),
+                                        TensorRequest::matrix(prefix + ".dkv", rank_ + rot_, hidden_), TensorRequest::vector(prefix + ".dkv.norm", rank_).with_init("one"),
                                         TensorRequest::matrix(prefix + ".uk", (long long)heads_ * dim_, rank_),
                                         TensorRequest::matrix(prefix + ".uv", (long long)heads_ * vdim_, rank_), TensorRequest::matrix(prefix + ".o", hidden_, (long long)heads_ * vdim_)};
-        if (sink_) r.push_back(TensorRequest::vector(prefix + ".sink", heads_));
+        if (sink_) r.push_back(TensorRequest::vector(prefix + ".sink", heads_).with_init("zero"));
         return r;
     }
     void load(const HostTensors& file, DType dtype) override {
@@ -269,7 +269,7 @@ public:
                                                prefix + ".shared");
     }
     std::vector<TensorRequest> tensor_requests() const override {
-        std::vector<TensorRequest> r = {TensorRequest::matrix(prefix + ".router", experts_ + identity_, hidden_), TensorRequest::vector(prefix + ".correction", experts_ + identity_)};
+        std::vector<TensorRequest> r = {TensorRequest::matrix(prefix + ".router", experts_ + identity_, hidden_), TensorRequest::vector(prefix + ".correction", experts_ + identity_).with_init("zero")};
         for (int e = 0; e < experts_; ++e) {
             const std::string ep = prefix + ".e" + std::to_string(e);
             r.push_back(TensorRequest::matrix(ep + ".gate", ff_, hidden_));
@@ -278,7 +278,7 @@ public:
         }
         if (shared_) {
             for (auto& t : shared_->tensor_requests()) r.push_back(t);
-            r.push_back(TensorRequest{prefix + ".shared.sg", {{1, hidden_}, {hidden_}}, false});
+            r.push_back(TensorRequest{prefix + ".shared.sg", {{1, hidden_}, {hidden_}}, false, ""});
         }
         return r;
     }
@@ -317,7 +317,7 @@ public:
     }
     size_t arena_bytes(long long T) const override {
         const size_t sorted = (size_t)grouped_rows(T) * ((size_t)hidden_ + ff_) * 2 + (size_t)grouped_rows(T) / 32 + (size_t)experts_ * 16;
-        return (size_t)T * ((size_t)top_ * (12 + (size_t)ff_ * 4) + 4 + (size_t)hidden_ * 8 + (size_t)shared_ff_ * 3 * 4) + sorted + (1u << 16);
+        return (size_t)T * ((size_t)top_ * (12 + (size_t)ff_ * 4) + 4 + (size_t)(experts_ + identity_) * 4 + (size_t)hidden_ * 8 + (size_t)shared_ff_ * 3 * 4) + sorted + (1u << 16);
     }
     // rows of the sorted copy of a step of T tokens: every expert's run starts at a multiple of 128
     int grouped_rows(long long T) const { return (int)((T * top_ + 127) / 128 * 128 + 128LL * experts_); }
@@ -330,8 +330,9 @@ public:
         int* ids = ctx.take<int>((size_t)T * top_);
         float* weights = ctx.take<float>((size_t)T * top_);
         float* gate = shared_ ? ctx.take<float>((size_t)T) : nullptr;
+        float* scores = ctx.take<float>((size_t)T * (experts_ + identity_));
         launch_check(eg_moe_route(ctx.stream, (int)dtype, h.p, h.ld, router_.as<float>(), correction_.as<float>(), shared_ ? shared_gate_.as<float>() : nullptr,
-                                  ids, weights, gate, T, hidden_, experts_ + identity_, top_), "moe_route");
+                                  scores, ids, weights, gate, T, hidden_, experts_ + identity_, top_), "moe_route");
         Delta shared;
         if (shared_) {
             PartInput rows;

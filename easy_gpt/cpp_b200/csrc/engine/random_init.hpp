@@ -87,7 +87,10 @@ inline void write_random_model(const std::string& folder, const std::string& con
         const bool gain = vector && ends_with(r.name, "norm.weight");
         for (size_t i = 0; i < n; ++i) {
             float v;
-            if (gain) v = 1.0f + (gain_std > 0 ? (float)(g.next() * gain_std) : 0.0f);
+            if (gain || r.init == "one") v = 1.0f + (gain_std > 0 ? (float)(g.next() * gain_std) : 0.0f);
+            else if (r.init == "zero") v = 0.0f;
+            else if (r.init == "log_decay") v = (float)std::log(1.0 + 15.0 * (0.5 + 0.5 * std::erf(g.next() / std::sqrt(2.0))));
+            else if (r.init == "step_bias") v = (float)std::log(std::expm1(std::pow(10.0, -3.0 + 2.0 * (0.5 + 0.5 * std::erf(g.next() / std::sqrt(2.0))))));
             else v = (float)(g.next() * (vector ? bias_std : std_dev));
             values[i] = float_to_bf16(v);
         }

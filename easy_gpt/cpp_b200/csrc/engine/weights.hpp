@@ -187,6 +187,14 @@ struct TensorRequest {
     std::string name;
     std::vector<std::vector<long long>> shapes;
     bool optional = false;
+    // what random-weights mode draws for it: "" a normal value, "one" / "zero" a constant, "log_decay" the logarithm of a
+    // decay rate between 1 and 16, "step_bias" the inverse softplus of a step size between 1e-3 and 1e-1
+    std::string init;
+    TensorRequest with_init(const char* how) const {
+        TensorRequest r = *this;
+        r.init = how;
+        return r;
+    }
     static TensorRequest matrix(const std::string& name, long long rows, long long cols) { return {name, {{rows, cols}}, false}; }
     // a [n, 1] vector is accepted like [n] (src/models/model_param_validation.cpp:62-74)
     static TensorRequest vector(const std::string& name, long long n) { return {name, {{n}, {n, 1}}, false}; }

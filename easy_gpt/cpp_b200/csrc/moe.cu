@@ -21,30 +21,33 @@
 
 namespace {
 
-// one block of four warps per token
+// grid (token, chunk of eight router outputs): a warp per output computes its logit (the output past the last one is the
+// shared expert's gate), so that a step of few tokens still fills the SMs
 template <typename T>
-__global__ void __launch_bounds__(128) moe_route_kernel(const T* __restrict__ h, long long ld, const float* __restrict__ router,
-                                                        const float* __restrict__ correction, const float* __restrict__ gate_w, int* __restrict__ ids,
-                                                        float* __restrict__ weights, float* __restrict__ gate, int width, int outputs, int top) {
-    extern __shared__ float sm[];                // [width] the token's row, [outputs] logits, then scores
-    float* row = sm;
-    float* logit = sm + width;
-    const int t = blockIdx.x;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    for (int j = threadIdx.x; j < width; j += blockDim.x) row[j] = to_f32<T>(h[(size_t)t * ld + j]);
-    __syncthreads();
-    for (int e = warp; e < outputs + (gate_w ? 1 : 0); e += 4) {
-        const float* w = e < outputs ? router + (size_t)e * width : gate_w;
-        float acc = 0.f;
-        for (int j = lane; j < width; j += 32) acc = fmaf(w[j], row[j], acc);
-        acc = warp_sum(acc);
-        if (lane == 0) {
-            if (e < outputs) logit[e] = acc;
-            else gate[t] = 1.0f / (1.0f + expf(-acc));
-        }
+__global__ void __launch_bounds__(256) moe_logits_kernel(const T* __restrict__ h, long long ld, const float* __restrict__ router,
+                                                         const float* __restrict__ gate_w, float* __restrict__ logits, float* __restrict__ gate, int width,
+                                                         int outputs) {
+    const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int e = blockIdx.y * (blockDim.x >> 5) + warp;
+    if (e >= outputs + (gate_w ? 1 : 0)) return;
+    const float* w = e < outputs ? router + (size_t)e * width : gate_w;
+    const T* row = h + (size_t)t * ld;
+    float acc = 0.f;
+#pragma unroll 8
+    for (int j = lane; j < width; j += 32) acc = fmaf(w[j], to_f32<T>(row[j]), acc);
+    acc = warp_sum(acc);
+    if (lane == 0) {
+        if (e < outputs) logits[(size_t)t * outputs + e] = acc;
+        else gate[t] = 1.0f / (1.0f + expf(-acc));
     }
-    __syncthreads();
-    if (warp != 0) return;
+}
+
+// a warp per token: softmax over the logits (left in place as scores), then the `top` largest of score + correction
+__global__ void __launch_bounds__(128) moe_select_kernel(float* __restrict__ logits, const float* __restrict__ correction, int* __restrict__ ids,
+                                                         float* __restrict__ weights, int tokens, int outputs, int top) {
+    const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (t >= tokens) return;
+    float* logit = logits + (size_t)t * outputs;
     float top_logit = -INFINITY;
     for (int e = lane; e < outputs; e += 32) top_logit = fmaxf(top_logit, logit[e]);
     top_logit = warp_max(top_logit);
@@ -53,12 +56,12 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const T* __restrict__ h,
     sum = warp_sum(sum);
     for (int e = lane; e < outputs; e += 32) logit[e] = expf(logit[e] - top_logit) / sum;      // now the scores s
     __syncwarp();
-    unsigned long long taken_lo = 0ull;          // lanes track which of their own outputs are taken: bit k for e = lane + 32 k
+    unsigned long long taken = 0ull;             // a lane tracks which of its own outputs are taken: bit k for e = lane + 32 k
     for (int k = 0; k < top; ++k) {
         float best = -INFINITY;
         int arg = 0x7fffffff;
         for (int e = lane, i = 0; e < outputs; e += 32, ++i) {
-            if (i < 64 && (taken_lo >> i) & 1ull) continue;
+            if ((taken >> i) & 1ull) continue;
             const float v = logit[e] + correction[e];
             if (v > best) { best = v; arg = e; }
         }
@@ -67,7 +70,7 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const T* __restrict__ h,
             const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
             if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
         }
-        if (arg != 0x7fffffff && arg % 32 == lane) taken_lo |= 1ull << (arg / 32);
+        if (arg != 0x7fffffff && arg % 32 == lane) taken |= 1ull << (arg / 32);
         if (lane == 0) {
             ids[(size_t)t * top + k] = arg == 0x7fffffff ? outputs : arg;
             weights[(size_t)t * top + k] = arg == 0x7fffffff ? 0.f : logit[arg];
@@ -92,9 +95,28 @@ __global__ void __launch_bounds__(256) moe_hidden_kernel(const T* __restrict__ h
     const T* g = GU + ((size_t)e * 2 * ff + 2 * f) * width;
     const T* u = g + width;
     float ag = 0.f, au = 0.f;
-    for (int j = lane; j < width; j += 32) {
-        ag = fmaf(to_f32<T>(g[j]), row[j], ag);
-        au = fmaf(to_f32<T>(u[j]), row[j], au);
+    if (sizeof(T) == 2 && width % 8 == 0) {                      // eight weights a load
+        const uint4* g8 = reinterpret_cast<const uint4*>(g);
+        const uint4* u8 = reinterpret_cast<const uint4*>(u);
+#pragma unroll 2
+        for (int j = lane; j < width / 8; j += 32) {
+            const uint4 gv = g8[j], uv = u8[j];
+            const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(&gv);
+            const __nv_bfloat162* up = reinterpret_cast<const __nv_bfloat162*>(&uv);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const float2 gf = __bfloat1622float2(gp[q]), uf = __bfloat1622float2(up[q]);
+                ag = fmaf(gf.x, row[8 * j + 2 * q], ag);
+                ag = fmaf(gf.y, row[8 * j + 2 * q + 1], ag);
+                au = fmaf(uf.x, row[8 * j + 2 * q], au);
+                au = fmaf(uf.y, row[8 * j + 2 * q + 1], au);
+            }
+        }
+    } else {
+        for (int j = lane; j < width; j += 32) {
+            ag = fmaf(to_f32<T>(g[j]), row[j], ag);
+            au = fmaf(to_f32<T>(u[j]), row[j], au);
+        }
     }
     ag = warp_sum(ag);
     au = warp_sum(au);
@@ -122,7 +144,24 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const T* __restrict__ 
         const T* d = Dn + ((size_t)e * width + j) * ff;
         const T* a = act + ((size_t)t * top + k) * ff;
         float acc = 0.f;
-        for (int f = lane; f < ff; f += 32) acc = fmaf(to_f32<T>(d[f]), to_f32<T>(a[f]), acc);
+        if (sizeof(T) == 2 && ff % 8 == 0) {                     // eight weights a load
+            const uint4* d8 = reinterpret_cast<const uint4*>(d);
+            const uint4* a8 = reinterpret_cast<const uint4*>(a);
+#pragma unroll 2
+            for (int f = lane; f < ff / 8; f += 32) {
+                const uint4 dv = d8[f], av = a8[f];
+                const __nv_bfloat162* dp = reinterpret_cast<const __nv_bfloat162*>(&dv);
+                const __nv_bfloat162* ap = reinterpret_cast<const __nv_bfloat162*>(&av);
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const float2 df = __bfloat1622float2(dp[q]), af = __bfloat1622float2(ap[q]);
+                    acc = fmaf(df.x, af.x, acc);
+                    acc = fmaf(df.y, af.y, acc);
+                }
+            }
+        } else {
+            for (int f = lane; f < ff; f += 32) acc = fmaf(to_f32<T>(d[f]), to_f32<T>(a[f]), acc);
+        }
         total += wgt * warp_sum(acc);
     }
     if (shared) {
@@ -135,16 +174,15 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const T* __restrict__ 
 }  // namespace
 
 // ids [T, top] int32 (router outputs; those >= the number of experts stand for the identity), weights [T, top] float32,
-// gate [T] float32 (only with gate_w)
+// gate [T] float32 (only with gate_w); logits [T, outputs] float32 is scratch (it ends up holding the scores)
 EG_API int eg_moe_route(cudaStream_t stream, int dtype, const void* h, long long ld, const float* router, const float* correction, const float* gate_w,
-                        int* ids, float* weights, float* gate, int tokens, int width, int outputs, int top) {
+                        float* logits, int* ids, float* weights, float* gate, int tokens, int width, int outputs, int top) {
     if (tokens <= 0) return 0;
-    const size_t smem = (size_t)(width + outputs) * sizeof(float);
-    if (top < 1 || top > outputs || outputs > 2048 || smem > 48 * 1024) return (int)cudaErrorInvalidValue;
-    if (dtype == EG_BF16)
-        moe_route_kernel<bf16><<<tokens, 128, smem, stream>>>((const bf16*)h, ld, router, correction, gate_w, ids, weights, gate, width, outputs, top);
-    else
-        moe_route_kernel<float><<<tokens, 128, smem, stream>>>((const float*)h, ld, router, correction, gate_w, ids, weights, gate, width, outputs, top);
+    if (top < 1 || top > outputs || outputs > 2048 || !logits) return (int)cudaErrorInvalidValue;
+    dim3 grid(tokens, (outputs + (gate_w ? 1 : 0) + 7) / 8);
+    if (dtype == EG_BF16) moe_logits_kernel<bf16><<<grid, 256, 0, stream>>>((const bf16*)h, ld, router, gate_w, logits, gate, width, outputs);
+    else moe_logits_kernel<float><<<grid, 256, 0, stream>>>((const float*)h, ld, router, gate_w, logits, gate, width, outputs);
+    moe_select_kernel<<<(tokens + 3) / 4, 128, 0, stream>>>(logits, correction, ids, weights, tokens, outputs, top);
     return eg_launch_status();
 }
 
