@@ -232,25 +232,40 @@ __global__ void __launch_bounds__(WARPS * 32) attention_latent_mma_kernel(const 
     }
 }
 
-// one block per (token, head): the parts' maxima, sums and weighted sums and the sink become the output row
+// one block per (token, head): the parts' maxima, sums and weighted sums and the sink become the output row.  The parts'
+// factors are worked out once, side by side (a thread per part), before the row is summed.
 __global__ void attention_latent_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, const float* __restrict__ sink,
                                               bf16* __restrict__ out, int heads, int rank, int splits) {
+    __shared__ float factor[64];
+    __shared__ float inv_denom;
     const size_t row = blockIdx.x;
     const int head = (int)(row % heads);
-    float top = sink ? sink[head] : -INFINITY;
-    for (int s = 0; s < splits; ++s) top = fmaxf(top, part_ml[(row * splits + s) * 2]);
-    float denom = sink ? expf(sink[head] - top) : 0.f;
-    for (int s = 0; s < splits; ++s) {
-        const float m = part_ml[(row * splits + s) * 2];
-        if (m != -INFINITY) denom += part_ml[(row * splits + s) * 2 + 1] * expf(m - top);
+    if (threadIdx.x < 32) {
+        const int lane = threadIdx.x;
+        float m[2], l[2];
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+            const int s = lane + 32 * q;
+            m[q] = s < splits ? part_ml[(row * splits + s) * 2] : -INFINITY;
+            l[q] = s < splits ? part_ml[(row * splits + s) * 2 + 1] : 0.f;
+        }
+        const float sk = sink ? sink[head] : -INFINITY;
+        const float top = fmaxf(sk, warp_max(fmaxf(m[0], m[1])));
+        float sum = 0.f;
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+            const float f = m[q] == -INFINITY ? 0.f : expf(m[q] - top);
+            factor[lane + 32 * q] = f;
+            sum += l[q] * f;
+        }
+        sum = warp_sum(sum) + (sink ? expf(sk - top) : 0.f);
+        if (lane == 0) inv_denom = 1.0f / sum;
     }
+    __syncthreads();
     for (int d = threadIdx.x; d < rank; d += blockDim.x) {
         float v = 0.f;
-        for (int s = 0; s < splits; ++s) {
-            const float m = part_ml[(row * splits + s) * 2];
-            if (m != -INFINITY) v = fmaf(part_o[(row * splits + s) * rank + d], expf(m - top), v);
-        }
-        out[row * rank + d] = __float2bfloat16_rn(v / denom);
+        for (int s = 0; s < splits; ++s) v = fmaf(part_o[(row * splits + s) * rank + d], factor[s], v);
+        out[row * rank + d] = __float2bfloat16_rn(v * inv_denom);
     }
 }
 
@@ -290,7 +305,7 @@ EG_API int eg_attention_latent_mma(cudaStream_t stream, const void* qa, const vo
                                    const int* positions, const float* sink, void* out, float* part_o, float* part_ml, int tokens, int heads, int rank, int rot,
                                    int page_size, long long page_stride, int num_pages, int splits, int* status) {
     if (tokens <= 0) return 0;
-    if (!eg_attention_latent_mma_takes(rank, rot) || splits < 1 || (splits > 1 && (!part_o || !part_ml)) || page_stride % 8 || (uintptr_t)cache % 16)
+    if (!eg_attention_latent_mma_takes(rank, rot) || splits < 1 || splits > 64 || (splits > 1 && (!part_o || !part_ml)) || page_stride % 8 || (uintptr_t)cache % 16)
         return (int)cudaErrorInvalidValue;
     const int D = rank + rot, DS = (D + 15) / 16 * 16 + 8;
     const size_t smem = (size_t)(16 + KT) * DS * 2 + 16 * (KT + 8) * 2 + 2 * WARPS * 16 * 4;
