@@ -172,15 +172,23 @@ inline bool moe_grouped_takes(DType dtype, int tokens, int width, int ff, int ex
     return dtype == DType::BF16 && tokens >= MOE_GROUPED_MIN_TOKENS && experts > 0 && width % 128 == 0 && ff % 64 == 0 && ff > 0;
 }
 
-// How many of a channel's states one thread of the selective scan keeps (1, 2, 4, ... 32): as many as still leave a
-// block of threads for every SM when one request is scanned alone.  It hangs off the mixer's sizes alone, never off the
+// How many of a channel's states one thread of the selective scan keeps (1, 2, 4, ... 32): as many as still leave four
+// blocks of threads for every SM when one request is scanned alone (the recurrence is bound by its latency: measured at
+// 4,096 channels x 16 states, a prompt of 2,048 tokens, ms for all layers' scans with 1 / 2 / 4 / 8 / 16 states a thread:
+// 1.8 / 2.3 / 4.0 / 7.2 / 13.6).  It hangs off the mixer's sizes alone, never off the
 // batch, so the order of the sum over a channel's states is the same in every step.
 inline int scan_states_per_lane(int channels, int states) {
+    static int forced = -1;                     // EASY_GPT_SCAN_STATES_PER_LANE, for measurements
+    if (forced < 0) {
+        const char* env = std::getenv("EASY_GPT_SCAN_STATES_PER_LANE");
+        forced = env ? std::atoi(env) : 0;
+    }
+    if (forced > 0) return forced;
     int spl = 32;
     while (spl > 1) {
         int lanes = 1;
         while (lanes * spl < states) lanes <<= 1;
-        if ((long long)channels * lanes >= 128LL * sm_count()) break;
+        if ((long long)channels * lanes >= 512LL * sm_count()) break;
         spl >>= 1;
     }
     while ((states + spl - 1) / spl > 32) spl *= 2;

@@ -273,3 +273,31 @@ def test_trace_replay_program(folders, tmp_path):
     want = pg.forward(cfg, w, toks)
     close(np.fromfile(out / "0.f32", dtype="<f4").reshape(2, -1), want[[0, 29]], "float32", "step 0")
     close(np.fromfile(out / "1.f32", dtype="<f4").reshape(1, -1), want[[39]], "float32", "step 1")
+
+
+def test_command_line_with_random_weights(tmp_path):
+    """The engine's own program on this design: random-weights mode writes a folder from a config.json (with the
+    per-tensor hints that keep norms, decays and step sizes sane), then prompts of token ids are decoded greedily; the
+    tokens must be the plain implementation's for the weights that were written."""
+    import json
+
+    cfg = model([(scan(inner=48, state=4, dt_rank=8, conv=3), routed(experts=3, identity=1, top=2, ff=32, shared=32)), (latent(), None)], width=64,
+                vocab=97, loop=(0, 2, 2))
+    (tmp_path / "config.json").write_text(json.dumps(cfg))
+    prompts = tmp_path / "prompts.txt"
+    prompts.write_text("5 17 3\n9,8,7,6\n")
+    folder = tmp_path / "model"
+    folder.mkdir()
+    cmd = [sys.executable, str(ROOT / "bin" / "easy_llm"), "--model", str(folder), "--random-weights", "7", "--config", str(tmp_path / "config.json"),
+           "--token-ids", "--greedy", "--max-steps", "10", "--dtype", "float32", "-f", str(prompts)]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr
+    outs = [[int(t) for t in line.split()] for line in (tmp_path / "prompts_output.txt").read_text().splitlines()]
+    assert len(outs) == 2 and len(outs[0]) == 8 and len(outs[1]) == 7
+    cfg_read, w = pg.read_model_dir(folder)
+    assert np.all(w["l0.norm1"] == 1.0) and np.all(w["l0.mix.D"] == 1.0) and np.all(w["l1.mix.sink"] == 0.0) and w["l0.mix.A_log"].min() >= 0.0
+    for prompt, out in zip([[5, 17, 3], [9, 8, 7, 6]], outs):
+        logits = pg.forward(cfg_read, w, prompt + out)
+        for i, tok in enumerate(out):
+            row = logits[len(prompt) + i - 1]
+            assert float(row.max() - row[tok]) <= 4e-4 * np.abs(row).max(), (i, tok, int(row.argmax()))
