@@ -54,7 +54,7 @@ ODD = model([(latent(heads=3, dim=12, rot_dim=6, vdim=10, kv_rank=20, q_rank=28,
              (scan(inner=40, state=3, dt_rank=1, conv=2), routed(experts=3, identity=0, top=3, ff=24, shared=0))], width=72, vocab=77, softcap=None)
 # sizes of one: one head, one state, one tap (no convolution state), one pass of a loop over everything, every output chosen
 ONES = model([(scan(inner=32, state=1, dt_rank=2, conv=1), routed(experts=2, identity=1, top=3, ff=16, shared=16)),
-              (latent(heads=1, dim=16, rot_dim=16, vdim=16, kv_rank=16, q_rank=16, scale=0.25), None)], width=48, vocab=64, loop=(0, 2, 1), softcap=30.0)
+              (latent(heads=1, dim=16, rot_dim=16, vdim=16, kv_rank=16, q_rank=16, scale=0.25), None)], width=48, vocab=64, loop=(0, 2, 1), softcap=20.0)
 
 
 def tokens(vocab, n, seed):
