@@ -112,9 +112,13 @@ def test_each_mechanism_alone(folders, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name,cfg", [("general", GENERAL), ("odd", ODD), ("ones", ONES)])
+@pytest.mark.parametrize("name,cfg", [("general", GENERAL), ("odd", ODD), ("ones", ONES), ("alone_scan_wide_rank", None), ("alone_routed_grouped", None),
+                                      ("alone_latent_many_heads", None), ("alone_latent_wide", None)])
 def test_prompt_whole_and_token_by_token(folders, name, cfg, dtype):
-    folder, cfg, w = folders(name, cfg, seed=5)
+    if cfg is None:                                  # the single-mechanism models whose decode steps take other kernels than their prompts
+        name = name[len("alone_"):]
+        cfg = ALONE[name]
+    folder, cfg, w = folders(name, cfg, seed=3 if name in ALONE else 5)
     toks = tokens(cfg["vocab"], 70, 2)
     want = pg.forward(cfg, w, toks)
     r = runner(folder, dtype)
