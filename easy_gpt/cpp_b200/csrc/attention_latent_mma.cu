@@ -53,10 +53,13 @@ __global__ void __launch_bounds__(WARPS * 32) attention_latent_mma_kernel(const 
     const int* table = block_table + (size_t)token_seq[t] * table_stride;
 
     // queries (zero rows for heads past the last one, zero columns past D), and the key tile's padding columns
-    for (int i = threadIdx.x; i < 16 * DS; i += blockDim.x) {
-        const int h = i / DS, d = i % DS;
-        Qs[i] = (head0 + h < heads && d < D) ? qa[((size_t)t * heads + head0 + h) * D + d] : __float2bfloat16(0.f);
+    for (int i = threadIdx.x; i < 16 * (D / 8); i += blockDim.x) {          // 16 bytes a load
+        const int h = i / (D / 8), c = i % (D / 8);
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (head0 + h < heads) v = *reinterpret_cast<const uint4*>(qa + ((size_t)t * heads + head0 + h) * D + c * 8);
+        *reinterpret_cast<uint4*>(Qs + h * DS + c * 8) = v;
     }
+    for (int i = threadIdx.x; i < 16 * (DS - D); i += blockDim.x) Qs[(i / (DS - D)) * DS + D + i % (DS - D)] = __float2bfloat16(0.f);
     for (int i = threadIdx.x; i < KT * (DS - D); i += blockDim.x) Ks[(i / (DS - D)) * DS + D + i % (DS - D)] = __float2bfloat16(0.f);
 
     float o[PAIRS][2][4];
@@ -305,7 +308,7 @@ EG_API int eg_attention_latent_mma(cudaStream_t stream, const void* qa, const vo
                                    const int* positions, const float* sink, void* out, float* part_o, float* part_ml, int tokens, int heads, int rank, int rot,
                                    int page_size, long long page_stride, int num_pages, int splits, int* status) {
     if (tokens <= 0) return 0;
-    if (!eg_attention_latent_mma_takes(rank, rot) || splits < 1 || splits > 64 || (splits > 1 && (!part_o || !part_ml)) || page_stride % 8 || (uintptr_t)cache % 16)
+    if (!eg_attention_latent_mma_takes(rank, rot) || splits < 1 || splits > 64 || (splits > 1 && (!part_o || !part_ml)) || page_stride % 8 || (uintptr_t)cache % 16 || (uintptr_t)qa % 16)
         return (int)cudaErrorInvalidValue;
     const int D = rank + rot, DS = (D + 15) / 16 * 16 + 8;
     const size_t smem = (size_t)(16 + KT) * DS * 2 + 16 * (KT + 8) * 2 + 2 * WARPS * 16 * 4;

@@ -310,8 +310,7 @@ inline ModelSpec gufanex_spec(const json::Value& config) {
                     e.add_embedding = t > 0;
                 }
             }
-    for (long long i = std::max(stop, start); i < n; ++i)
-        if (i >= stop) run(i);
+    for (long long i = stop; i < n; ++i) run(i);
     spec.embedding = PartSpec{"embedding", Params{{"vocab_size", vocab}, {"hidden_size", width}, {"weight_name", ""}}, "embed", true};
     spec.final_norm = layer_norm("final.norm");
     Params head{{"vocab_size", vocab}, {"hidden_size", width}, {"weight_name", ""}};

@@ -16,6 +16,7 @@
 //   FeedForward     forward(ctx, input, follow) -> Delta
 //   Norm            forward(ctx, residual, delta, ..., out, ...): residual += delta, out = normalised rows
 //   PositionEncoding  any of half_rotation(), apply_to_query_key(), add_to_embedding()
+//   StreamAdd       forward(ctx, residual, first, row): what a run entry adds to the stream before its layer
 //   StepContext     the step's batch: token ids, positions, token -> entry map, entry starts / cached lengths / state slots
 //                   (device arrays, and host twins outside captured steps), block tables and cache positions per group
 #pragma once
