@@ -323,12 +323,120 @@ inline ModelSpec gufanex_spec(const json::Value& config) {
     return spec;
 }
 
+// ---- Lasizen ---------------------------------------------------------------------------------------------------------------
+// A decoder whose config.json lists its layers one by one ("type": "attention", attention over a sliding window with a
+// sink, or "delta", a gated delta-rule mixer; "mlp": a dense feed-forward, or null).  Both branches of a layer are normed
+// on both sides, x = x + norm1b(mixer(shift(norm1(x)))), x = x + norm2b(ff(norm2(x))), all RMS norms; in front of the mixer
+// every token's normed row is mixed with that of the token in front of it (a learned weight per channel).  A run of
+// layers ("loop": start, stop, times) is passed through several times in a row with the same weights and a cache or state
+// of its own per pass.  The embedding is scaled by embedding.scale, the logits by logit_scale.  Every size and constant is
+// a key of config.json; tensor names are "l<i>.<part>.<tensor>".
+inline ModelSpec lasizen_spec(const json::Value& config) {
+    using C = GufanexConfig;        // the typed readers (a key's path goes into the refusal)
+    if (!config.is_object()) throw ConfigError("config.json is not a JSON object");
+    ModelSpec spec;
+    spec.architecture = "lasizen";
+    const long long width = C::integer(config, "width", ""), vocab = C::integer(config, "vocab", "");
+    if (width <= 0 || vocab <= 0) throw ConfigError("width and vocab must be > 0");
+    const double eps = C::number(C::need(config, "norm", ""), "eps", "norm.");
+    if (eps <= 0.0) throw ConfigError("norm.eps must be > 0");
+    spec.vocab_size = vocab;
+    spec.hidden_size = width;
+    spec.max_positions = C::integer_or(config, "max_positions", 1LL << 30, "");     // the design sets no limit; positions are 32-bit
+    auto norm = [&](const std::string& name) { return PartSpec{"rmsnorm", Params{{"size", width}, {"eps", eps}, {"weight_name", ""}}, name, true}; };
+    const json::Value& layers = C::need(config, "layers", "");
+    if (!layers.is_array() || layers.array.empty()) throw ConfigError("layers must be a list with at least one layer");
+    for (size_t i = 0; i < layers.array.size(); ++i) {
+        const json::Value& l = layers.array[i];
+        const std::string where = "layers[" + std::to_string(i) + "].", prefix = "l" + std::to_string(i), w = where + "mixer.";
+        const json::Value& type = C::need(l, "type", where);
+        const json::Value& m = C::need(l, "mixer", where);
+        if (!type.is_string()) throw ConfigError(where + "type must be a string");
+        LayerSpec layer;
+        PartSpec mixer;
+        const long long heads = C::integer(m, "heads", w), kv_heads = C::integer(m, "kv_heads", w), dim = C::integer(m, "dim", w), vdim = C::integer(m, "vdim", w);
+        if (heads <= 0 || kv_heads <= 0 || dim <= 0 || vdim <= 0 || heads % kv_heads)
+            throw ConfigError(w + "heads, kv_heads, dim and vdim must be > 0, heads a multiple of kv_heads");
+        if (type.string == "attention") {
+            Params a{{"hidden_size", width}, {"heads", heads}, {"kv_heads", kv_heads}, {"dim", dim}, {"vdim", vdim}, {"scale", C::number(m, "scale", w)},
+                     {"sink_logit", 0.0}, {"unit_eps", eps}};
+            if (C::present(m, "mask")) {
+                const long long size = C::integer(*m.find("mask"), "size", w + "mask.");
+                if (size <= 0) throw ConfigError(w + "mask.size must be > 0");
+                a.set("window", size);
+            }
+            mixer = PartSpec{"sink_attention", a, prefix + ".mix", true};
+            if (C::present(m, "rot")) {
+                const json::Value& rot = *m.find("rot");
+                const long long dims = C::integer(rot, "dims", w + "rot.");
+                if (dims < 0 || dims % 2 || dims > dim) throw ConfigError(w + "rot.dims must be even and within dim");
+                if (dims > 0) {
+                    Params r{{"head_dim", dim}, {"rotary_dim", dims}, {"theta", C::number(rot, "base", w + "rot.")}};
+                    if (C::present(rot, "scaling")) {
+                        const json::Value& sc = *rot.find("scaling");
+                        const std::string ws = w + "rot.scaling.";
+                        r.set("scaling_factor", C::number(sc, "factor", ws));
+                        r.set("scaling_original", C::number(sc, "original", ws));
+                        r.set("scaling_fast", C::number(sc, "fast", ws));
+                        r.set("scaling_slow", C::number(sc, "slow", ws));
+                    }
+                    layer.position = PartSpec{"rope", r, "", true};
+                }
+            }
+        } else if (type.string == "delta") {
+            mixer = PartSpec{"gated_delta", Params{{"hidden_size", width}, {"heads", heads}, {"kv_heads", kv_heads}, {"dim", dim}, {"vdim", vdim},
+                                                   {"conv", C::integer(m, "conv", w)}, {"eps", eps}, {"unit_eps", 1e-6}}, prefix + ".mix", true};
+        } else {
+            throw ConfigError(where + "type '" + type.string + "' is no mixer of this design (attention, delta)");
+        }
+        SubLayerSpec mix{"mixer", mixer, norm(prefix + ".norm1"), "pre", norm(prefix + ".norm1b")};
+        mix.shift = PartSpec{"token_shift", Params{{"size", width}}, prefix + ".shift", true};
+        layer.sublayers.push_back(std::move(mix));
+        if (C::present(l, "mlp")) {
+            const json::Value& mlp = *l.find("mlp");
+            const std::string wm = where + "mlp.";
+            const json::Value& kind = C::need(mlp, "kind", wm);
+            if (!kind.is_string() || kind.string != "dense") throw ConfigError(wm + "kind must be 'dense'");
+            const long long ff = C::integer(mlp, "ff", wm);
+            if (ff <= 0) throw ConfigError(wm + "ff must be > 0");
+            layer.sublayers.push_back({"feed_forward", PartSpec{"xielu", Params{{"hidden_size", width}, {"ff", ff}}, prefix + ".mlp", true}, norm(prefix + ".norm2"),
+                                       "pre", norm(prefix + ".norm2b")});
+        }
+        spec.layers.push_back(std::move(layer));
+    }
+    // the run order: the layers in front of the loop, the loop's layers `times` times (a cache or state per pass), the rest
+    const long long n = (long long)spec.layers.size();
+    long long start = n, stop = n, times = 1;
+    if (C::present(config, "loop")) {
+        const json::Value& loop = *config.find("loop");
+        start = C::integer(loop, "start", "loop.");
+        stop = C::integer(loop, "stop", "loop.");
+        times = C::integer(loop, "times", "loop.");
+        if (start < 0 || stop < start || stop > n || times < 1) throw ConfigError("loop must have 0 <= start <= stop <= layers and times >= 1");
+    }
+    int cache = 0;
+    auto run = [&](long long layer) { spec.run_order.push_back(RunEntry{(int)layer, cache++, true}); };
+    for (long long i = 0; i < std::min(start, n); ++i) run(i);
+    for (long long t = 0; t < times; ++t)
+        for (long long i = start; i < stop; ++i) run(i);
+    for (long long i = stop; i < n; ++i) run(i);
+    Params embedding{{"vocab_size", vocab}, {"hidden_size", width}, {"weight_name", ""}};
+    if (C::present(config, "embedding")) embedding.set("scale", C::number(*config.find("embedding"), "scale", "embedding."));
+    spec.embedding = PartSpec{"embedding", embedding, "embed", true};
+    spec.final_norm = norm("final.norm");
+    Params head{{"vocab_size", vocab}, {"hidden_size", width}, {"weight_name", ""}};
+    if (C::present(config, "logit_scale")) head.set("scale", C::number(config, "logit_scale", ""));
+    spec.lm_head = PartSpec{"lm_head", head, "head", true};
+    return spec;
+}
+
 inline void register_builtin_architectures() {
     ArchitectureRegistry& r = ArchitectureRegistry::instance();
     for (auto& e : r.entries)
         if (e.first == "qwen2") return;
     r.add("qwen2", qwen2_spec);
     r.add("gufanex", gufanex_spec);
+    r.add("lasizen", lasizen_spec);
 }
 
 }  // namespace easygpt::engine

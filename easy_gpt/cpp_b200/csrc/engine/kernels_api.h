@@ -125,4 +125,24 @@ int eg_attention_latent_mma_takes(int rank, int rot);
 int eg_attention_latent_mma(cudaStream_t stream, const void* qa, const void* cache, const int* block_table, int table_stride, const int* token_seq, const int* positions, const float* sink, void* out, float* part_o, float* part_ml, int tokens, int heads, int rank, int rot, int page_size, long long page_stride, int num_pages, int splits, int* status);
 // attention_latent_mma.cu
 int eg_latent_rotate_query(cudaStream_t stream, const void* q, long long ldq, const int* positions, const float* inv_freq, int rot_dims, float scale, void* qa, int tokens, int heads, int dim, int rot, int rank);
+// sandwich.cu
+int eg_token_shift(cudaStream_t stream, const float* rows, const float* mu, float* state, long long slot_floats, const int* token_seq, const int* seq_starts, const int* seq_slots, void* out, int out_dtype, int tokens, int hidden);
+// sandwich.cu
+int eg_rmsnorm_shift(cudaStream_t stream, const float* residual, const float* gain, float eps, const float* mu, float* state, long long slot_floats, const int* token_seq, const int* seq_starts, const int* seq_slots, void* out, int out_dtype, int tokens, int hidden);
+// sandwich.cu
+int eg_rmsnorm_add(cudaStream_t stream, float* residual, const void* y, int y_dtype, long long ldy, const float* gain, float eps, int tokens, int hidden);
+// sandwich.cu
+int eg_xielu(cudaStream_t stream, const void* x, int x_dtype, long long ldx, void* out, int out_dtype, long long ldo, int tokens, int n, float ap, float an);
+// sandwich.cu
+int eg_embedding_gather_scaled(cudaStream_t stream, int dtype, const int* ids, const void* table, float* residual, int tokens, int hidden, int vocab, float scale, int* status);
+// sandwich.cu
+int eg_scale_f32(cudaStream_t stream, float* x, long long n, float s);
+// attention_sink.cu
+int eg_sink_attention_prepare(cudaStream_t stream, int dtype, const float* proj, long long ld, const float* table, int rot_dims, float magnitude, const int* slot_map, void* cache, int page_size, long long page_stride, long long pool_slots, void* q_out, int tokens, int heads, int kv_heads, int dk, int dv, float unit_eps, int* status);
+// attention_sink.cu
+int eg_sink_attention(cudaStream_t stream, int dtype, const void* q, const void* cache, const int* block_table, int table_stride, const int* token_seq, const int* positions, const int* token_list, void* out, long long ldo, int num_tokens, int heads, int kv_heads, int dk, int dv, int page_size, long long page_stride, int num_pages, int window, float scale, int has_sink, float sink_logit, int* status);
+// gated_delta.cu
+int eg_gated_delta_plan(int dk, int dv, int* rows_per_lane, int* lanes);
+// gated_delta.cu
+int eg_gated_delta(cudaStream_t stream, const float* qkv, long long ldq, int q_col, int k_col, int v_col, const float* proj, long long ldp, int b_col, int a_col, int z_col, const float* a_log, const float* dt_bias, const float* norm_w, float* state, long long slot_floats, long long state_offset, const int* seq_starts, const int* seq_slots, void* y, int y_dtype, long long ldy, int num_seqs, int heads, int kv_heads, int dk, int dv, float unit_eps, float eps);
 }  // extern "C"

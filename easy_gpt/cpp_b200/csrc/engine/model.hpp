@@ -7,6 +7,7 @@
 
 #include "architectures.hpp"
 #include "parts.hpp"
+#include "parts_delta.hpp"
 #include "parts_sequence.hpp"
 
 namespace easygpt::engine {
@@ -15,6 +16,7 @@ namespace easygpt::engine {
 struct SubLayer {
     std::string role, placement;
     std::shared_ptr<Norm> norm, output_norm;
+    std::shared_ptr<Shift> shift;        // between the norm in front and the part
     std::shared_ptr<Mixer> mixer;
     std::shared_ptr<FeedForward> feed_forward;
     bool plain_pre_norm = false;        // x = x + part(norm(x)) with nothing behind the part: the shape whose add and norm the parts may fuse
@@ -22,6 +24,7 @@ struct SubLayer {
     std::vector<Part*> parts() const {
         std::vector<Part*> out;
         if (norm) out.push_back(norm.get());
+        if (shift) out.push_back(shift.get());
         out.push_back(part());
         if (output_norm) out.push_back(output_norm.get());
         return out;
@@ -52,7 +55,8 @@ public:
             } else {
                 sub.feed_forward = PartRegistry::find(reg.feed_forwards, "feed_forward", s.part.kind)(s.part.params, s.part.prefix);
             }
-            sub.plain_pre_norm = sub.norm && sub.placement == "pre" && !sub.output_norm;
+            if (s.shift.present) sub.shift = PartRegistry::find(reg.shifts, "shift", s.shift.kind)(s.shift.params, s.shift.prefix);
+            sub.plain_pre_norm = sub.norm && sub.placement == "pre" && !sub.output_norm && !sub.shift;
             sublayers.push_back(std::move(sub));
         }
     }
@@ -61,6 +65,13 @@ public:
         for (auto& s : sublayers)
             for (Part* p : s.parts()) out.push_back(p);
         return out;
+    }
+    // float32 values per request that the layer's own parts (its shifts) keep beside the mixer's cache or state
+    long long layer_state_floats() const {
+        long long n = 0;
+        for (auto& s : sublayers)
+            if (s.shift) n += s.shift->state_floats();
+        return n;
     }
     // the norm that a fused add + norm in front of this layer would have to be (nullptr: nothing in front may prepare it)
     const Norm* first_norm() const { return !parallel && sublayers.front().plain_pre_norm ? sublayers.front().norm.get() : nullptr; }
@@ -173,10 +184,30 @@ public:
             s.delta = Delta();
             PartInput in;
             in.rows = Rows{work, ctx.dtype, T, hidden, hidden};
-            if (sub.norm && sub.placement == "pre") sub.norm->forward(ctx, s.residual, nullptr, ctx.dtype, work, ctx.dtype, T, nullptr);
-            else launch_check(eg_convert_rows(ctx.stream, s.residual, (int)DType::F32, work, (int)ctx.dtype, n), "convert");
+            if (sub.shift) {
+                // norm, then the mix with the row in front: one kernel where the norm is a plain RMSNorm, else the normed
+                // rows in float32 and the shift behind them
+                if (!cache.layer_state || cache.layer_state_floats < sub.shift->state_floats()) throw DeviceError("a shift was handed no state of its size");
+                const float* gain = nullptr;
+                float eps = 0.f;
+                if (!(sub.norm->rms_parameters(&gain, &eps) &&
+                      sub.shift->forward_rms(ctx, s.residual, gain, eps, cache.layer_state, cache.layer_state_floats, work, ctx.dtype))) {
+                    float* normed = ctx.take<float>((size_t)n);
+                    sub.norm->forward(ctx, s.residual, nullptr, DType::F32, normed, DType::F32, T, nullptr);
+                    sub.shift->forward(ctx, normed, cache.layer_state, cache.layer_state_floats, work, ctx.dtype);
+                }
+            } else if (sub.norm && sub.placement == "pre") {
+                sub.norm->forward(ctx, s.residual, nullptr, ctx.dtype, work, ctx.dtype, T, nullptr);
+            } else {
+                launch_check(eg_convert_rows(ctx.stream, s.residual, (int)DType::F32, work, (int)ctx.dtype, n), "convert");
+            }
             Delta d = sub.mixer ? sub.mixer->forward(ctx, in, cache, nullptr) : sub.feed_forward->forward(ctx, in, nullptr);
             if (d.has_pre()) throw DeviceError("a part returned prepared rows without having been offered the norm that follows");
+            if (sub.output_norm && !(sub.norm && sub.placement == "post") && sub.output_norm->add_normed(ctx, s.residual, d.p, d.dtype, T)) {
+                // the branch's output went into the stream through its norm, in float32, in one kernel
+                s.delta = Delta();
+                continue;
+            }
             if (sub.output_norm) {
                 // norm(delta) in the compute dtype: through the float32 spare buffer
                 launch_check(eg_convert_rows(ctx.stream, d.p, (int)d.dtype, s.spare, (int)DType::F32, n), "convert");
@@ -216,6 +247,7 @@ public:
     Model(ModelSpec spec_, DType dtype) : spec(std::move(spec_)), dtype(dtype) {
         register_builtin_parts();
         register_sequence_parts();
+        register_delta_parts();
         spec.validate();
         PartRegistry& reg = PartRegistry::instance();
         embedding = PartRegistry::find(reg.embeddings, "embedding", spec.embedding.kind)(spec.embedding.params, spec.embedding.prefix);
@@ -288,7 +320,11 @@ public:
     // cache id -> what the entry that writes it needs
     std::map<int, CacheNeed> cache_needs() const {
         std::map<int, CacheNeed> needs;
-        auto need_of = [&](int layer) { return blocks[layer]->mixer ? blocks[layer]->mixer->cache_need() : CacheNeed(); };
+        auto need_of = [&](int layer) {
+            CacheNeed need = blocks[layer]->mixer ? blocks[layer]->mixer->cache_need() : CacheNeed();
+            need.layer_state_floats = blocks[layer]->layer_state_floats();
+            return need;
+        };
         for (auto& e : spec.run_order)
             if (e.writes_cache) needs[e.cache] = need_of(e.layer);
         for (auto& e : spec.run_order)

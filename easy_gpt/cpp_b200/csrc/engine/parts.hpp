@@ -187,10 +187,11 @@ private:
 // 1e-6, src/models/norm.cpp:41), fused with the float32 residual add ---------------------------------------------------
 class RMSNorm : public Norm {
 public:
-    RMSNorm(const Params& p, const std::string& prefix) : Norm(p, prefix), size_((int)p.integer("size")), eps_((float)p.real("eps")) {}
-    std::vector<TensorRequest> tensor_requests() const override { return {TensorRequest::vector(prefix + ".weight", size_)}; }
+    RMSNorm(const Params& p, const std::string& prefix)
+        : Norm(p, prefix), size_((int)p.integer("size")), eps_((float)p.real("eps")), weight_name_(prefix + p.text("weight_name", ".weight")) {}
+    std::vector<TensorRequest> tensor_requests() const override { return {TensorRequest::vector(weight_name_, size_).with_init("one")}; }
     void load(const HostTensors& file, DType) override {
-        const std::vector<float> g = host_floats(need_tensor(file, prefix + ".weight"));       // gains are used in float32 whatever they were stored in
+        const std::vector<float> g = host_floats(need_tensor(file, weight_name_));       // gains are used in float32 whatever they were stored in
         gain_ = upload(g.data(), g.size(), DType::F32);
     }
     size_t weight_bytes() const override { return (size_t)size_ * 4; }
@@ -205,11 +206,16 @@ public:
         launch_check(eg_add_rmsnorm(ctx.stream, (int)(delta ? delta_dtype : out_dtype), (int)out_dtype, residual, delta, rows, gain_.as<float>(), out,
                                     num_rows, size_, eps_), "add_rmsnorm");
     }
+    bool add_normed(const StepContext& ctx, float* residual, const void* y, DType y_dtype, int num_rows) const override {
+        launch_check(eg_rmsnorm_add(ctx.stream, residual, y, (int)y_dtype, size_, gain_.as<float>(), eps_, num_rows, size_), "rmsnorm_add");
+        return true;
+    }
     int size() const override { return size_; }
 
 private:
     int size_;
     float eps_;
+    std::string weight_name_;      // parameter weight_name: the gain's tensor name as a suffix of the prefix (default ".weight")
     DeviceBuffer gain_;
 };
 
@@ -276,34 +282,72 @@ private:
 };
 
 // ---- rotary position encoding, half rotation over rotary_dim dimensions of each head (src/ops.cpp:404-421).  The table
-// inv_freq[k] = theta^(-2k/rotary_dim) (src/ops.cpp:172-177) is built once on the host, in double, rounded to float32 -----
+// inv_freq[k] = theta^(-2k/rotary_dim) (src/ops.cpp:172-177) is built once on the host, in double, rounded to float32.
+// With scaling_factor s > 1 (and scaling_original L, scaling_fast b_f, scaling_slow b_s) the frequencies are stretched
+// for long contexts: with turn(b) = rotary_dim ln(L / (2 pi b)) / (2 ln theta), the index of the pair that makes b turns
+// over L positions, lo = max(floor(turn(b_f)), 0), hi = min(ceil(turn(b_s)), rotary_dim - 1),
+// r_k = clamp((k - lo) / max(hi - lo, 0.001), 0, 1), inv_freq[k] <- inv_freq[k] (r_k / s + 1 - r_k), and cos and sin
+// are multiplied by 0.1 ln s + 1 (HalfRotation::magnitude) -----
 class RotaryEncoding : public PositionEncoding {
 public:
     RotaryEncoding(const Params& p, const std::string& prefix)
         : PositionEncoding(p, prefix), head_dim_((int)p.integer("head_dim")), rotary_dim_((int)p.integer("rotary_dim", p.integer("head_dim"))),
-          theta_(p.real("theta")) {
+          theta_(p.real("theta")), factor_(p.has("scaling_factor") ? p.real("scaling_factor") : 0.0) {
         if (rotary_dim_ % 2 || rotary_dim_ <= 0 || rotary_dim_ > head_dim_)
             throw std::invalid_argument("rotary_dim " + std::to_string(rotary_dim_) + " must be even and within head_dim " + std::to_string(head_dim_));
         if (theta_ <= 0) throw std::invalid_argument("rope theta must be > 0");
+        if (factor_ != 0.0) {
+            original_ = p.real("scaling_original");
+            fast_ = p.real("scaling_fast");
+            slow_ = p.real("scaling_slow");
+            if (factor_ <= 0.0 || original_ <= 0.0 || fast_ <= 0.0 || slow_ <= 0.0 || theta_ == 1.0)
+                throw std::invalid_argument("a rotation's scaling needs positive factor, original, fast and slow, and a base other than 1");
+            magnitude_ = (float)(0.1 * std::log(factor_) + 1.0);
+        }
     }
     void load(const HostTensors&, DType) override {
         std::vector<float> inv(rotary_dim_ / 2);
-        for (int k = 0; k < rotary_dim_ / 2; ++k) inv[k] = (float)(1.0 / std::pow(theta_, 2.0 * k / rotary_dim_));
+        for (int k = 0; k < rotary_dim_ / 2; ++k) {
+            double f = 1.0 / std::pow(theta_, 2.0 * k / rotary_dim_);
+            if (factor_ != 0.0) {
+                auto turn = [&](double b) { return rotary_dim_ * std::log(original_ / (2.0 * M_PI * b)) / (2.0 * std::log(theta_)); };
+                const double lo = std::max(std::floor(turn(fast_)), 0.0), hi = std::min(std::ceil(turn(slow_)), (double)rotary_dim_ - 1.0);
+                const double ramp = std::min(1.0, std::max(0.0, (k - lo) / std::max(hi - lo, 0.001)));
+                f = f / factor_ * ramp + f * (1.0 - ramp);
+            }
+            inv[k] = (float)f;
+        }
         inv_freq_ = upload(inv.data(), inv.size(), DType::F32);
     }
     bool capturable() const override { return true; }
     bool half_rotation(HalfRotation* out) const override {
         out->inv_freq = inv_freq_.as<float>();
         out->rotary_dim = rotary_dim_;
+        out->magnitude = magnitude_;
         out->key = "rope:" + std::to_string(theta_) + ":" + std::to_string(rotary_dim_);
+        if (factor_ != 0.0) out->key += ":" + std::to_string(factor_) + ":" + std::to_string(original_) + ":" + std::to_string(fast_) + ":" + std::to_string(slow_);
         return true;
     }
 
 private:
     int head_dim_, rotary_dim_;
-    double theta_;
+    double theta_, factor_, original_ = 0.0, fast_ = 0.0, slow_ = 0.0;
+    float magnitude_ = 1.0f;
     DeviceBuffer inv_freq_;
 };
+
+// cos/sin [T, rotary_dim/2, 2] of this step's positions: computed by the first layer that asks and shared by every layer
+// whose rotation has the same key
+inline const float* step_rotation_table(const StepContext& ctx, const HalfRotation& rot) {
+    auto& shared = const_cast<StepContext&>(ctx).shared;
+    const std::string key = "rotation table " + rot.key;
+    auto it = shared.find(key);
+    if (it != shared.end()) return (const float*)it->second;
+    float* table = ctx.take_for_step<float>((size_t)ctx.num_tokens * rot.rotary_dim);
+    launch_check(eg_rope_table(ctx.stream, ctx.positions, rot.inv_freq, table, ctx.num_tokens, rot.rotary_dim / 2), "rope_table");
+    shared[key] = table;
+    return table;
+}
 
 // ---- grouped-query attention over the paged cache -----------------------------------------------------------------
 // Per token: q, k, v = x Wq^T + bq, ... (src/models/self_attn.cpp:225-227) as ONE product with the three weights
@@ -450,6 +494,7 @@ public:
         const long long pool_slots = (long long)cache.num_pages * cache.page_size;
         HalfRotation rot;
         const bool rotates = position && position->half_rotation(&rot);
+        if (rotates && rot.magnitude != 1.0f) throw DeviceError("this attention's kernels take no rotation with a factor on cos and sin");
         Rows qkv;
         if (in.pending && in.pending->fusable && cache.writes && rotates && rot.rotary_dim == head_dim_ &&
             (head_dim_ == 16 || head_dim_ == 32 || head_dim_ == 64 || head_dim_ == 128)) {
@@ -529,18 +574,7 @@ public:
     }
 
 private:
-    // cos/sin [T, rotary_dim/2, 2] of this step's positions: computed by the first layer that asks and shared by every
-    // layer whose rotation has the same key
-    static const float* rotation_table(const StepContext& ctx, const HalfRotation& rot) {
-        auto& shared = const_cast<StepContext&>(ctx).shared;
-        const std::string key = "rotation table " + rot.key;
-        auto it = shared.find(key);
-        if (it != shared.end()) return (const float*)it->second;
-        float* table = ctx.take_for_step<float>((size_t)ctx.num_tokens * rot.rotary_dim);
-        launch_check(eg_rope_table(ctx.stream, ctx.positions, rot.inv_freq, table, ctx.num_tokens, rot.rotary_dim / 2), "rope_table");
-        shared[key] = table;
-        return table;
-    }
+    static const float* rotation_table(const StepContext& ctx, const HalfRotation& rot) { return step_rotation_table(ctx, rot); }
     void paged(const StepContext& ctx, const Rows& qkv, const CacheView& cache, const GroupTables& tables, const Rows& attn, int tokens, int splits,
                int window, const int* seq_context, const int* token_list) const {
         float *acc = nullptr, *ml = nullptr;
@@ -681,7 +715,8 @@ private:
 class TokenEmbedding : public Embedding {
 public:
     TokenEmbedding(const Params& p, const std::string& prefix)
-        : Embedding(p, prefix), vocab_((int)p.integer("vocab_size")), hidden_((int)p.integer("hidden_size")), weight_name_(prefix + p.text("weight_name", ".weight")) {}
+        : Embedding(p, prefix), vocab_((int)p.integer("vocab_size")), hidden_((int)p.integer("hidden_size")), weight_name_(prefix + p.text("weight_name", ".weight")),
+          scale_(p.has("scale") ? (float)p.real("scale") : 1.0f) {}
     std::vector<TensorRequest> tensor_requests() const override { return {TensorRequest::matrix(weight_name_, vocab_, hidden_)}; }
     void load(const HostTensors& file, DType dtype) override {
         table_ = upload(need_tensor(file, weight_name_), dtype);
@@ -689,12 +724,17 @@ public:
     }
     bool capturable() const override { return true; }
     void forward(const StepContext& ctx, float* residual) override {
+        if (scale_ != 1.0f) {       // residual[t] = scale * E[id[t]]
+            launch_check(eg_embedding_gather_scaled(ctx.stream, (int)dtype_, ctx.token_ids, table_.get(), residual, ctx.num_tokens, hidden_, vocab_, scale_,
+                                                    ctx.status), "embedding_gather_scaled");
+            return;
+        }
         launch_check(eg_embedding_gather(ctx.stream, (int)dtype_, ctx.token_ids, table_.get(), residual, ctx.num_tokens, hidden_, vocab_, ctx.status),
                      "embedding_gather");
     }
     const void* table() const override { return table_.get(); }
     bool fused_gather(const void** table, int* vocab) const override {
-        if (dtype_ != DType::BF16 || hidden_ % 4) return false;
+        if (dtype_ != DType::BF16 || hidden_ % 4 || scale_ != 1.0f) return false;
         *table = table_.get();
         *vocab = vocab_;
         return true;
@@ -703,6 +743,7 @@ public:
 private:
     int vocab_, hidden_;
     std::string weight_name_;
+    float scale_;                   // parameter scale: a factor on every embedding row (default 1)
     DType dtype_ = DType::BF16;
     DeviceBuffer table_;
 };
@@ -715,7 +756,8 @@ class LMHead : public Head {
 public:
     LMHead(const Params& p, const std::string& prefix)
         : Head(p, prefix), vocab_((int)p.integer("vocab_size")), hidden_((int)p.integer("hidden_size")), tied_(p.has("tied_to")),
-          softcap_(p.has("softcap") ? (float)p.real("softcap") : 0.f), weight_name_(prefix + p.text("weight_name", ".weight")) {
+          softcap_(p.has("softcap") ? (float)p.real("softcap") : 0.f), scale_(p.has("scale") ? (float)p.real("scale") : 1.0f),
+          weight_name_(prefix + p.text("weight_name", ".weight")) {
         if (softcap_ < 0.f) throw std::invalid_argument("softcap must be positive");
     }
     std::vector<TensorRequest> tensor_requests() const override {
@@ -730,7 +772,7 @@ public:
     bool capturable() const override { return true; }
     int vocab() const override { return vocab_; }
     bool emit_fused(FusedBuilder& b, const float* gain, float eps) const override {
-        if (b.ctx->dtype != DType::BF16 || hidden_ != b.hidden || linear_.has_bias() || softcap_ > 0.f) return false;
+        if (b.ctx->dtype != DType::BF16 || hidden_ != b.hidden || linear_.has_bias() || softcap_ > 0.f || scale_ != 1.0f) return false;
         b.logits = b.arena->take_n<float>((size_t)b.tokens * vocab_);
         EgFusedTemplate t = FusedBuilder::blank();
         t.input = EGF_IN_NORM;
@@ -752,6 +794,7 @@ public:
         Rows x = in.pending ? in.pending->materialize() : in.rows;
         x.rows = rows;
         float* logits = (float*)linear_(ctx, x, /*out_f32=*/true).p;
+        if (scale_ != 1.0f) launch_check(eg_scale_f32(ctx.stream, logits, (long long)rows * vocab_, scale_), "scale");
         // logits <- cap * tanh(logits / cap), where the model has such a cap
         if (softcap_ > 0.f) launch_check(eg_softcap(ctx.stream, logits, (long long)rows * vocab_, softcap_), "softcap");
         return logits;
@@ -760,7 +803,7 @@ public:
 private:
     int vocab_, hidden_;
     bool tied_;
-    float softcap_;
+    float softcap_, scale_;         // parameter scale: logits <- scale * logits (before a soft cap), default 1
     std::string weight_name_;
     Linear linear_;
 };

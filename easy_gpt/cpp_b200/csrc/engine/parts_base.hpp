@@ -39,9 +39,14 @@ struct CacheNeed {
     long long window = -1;                  // PagedKV: < 0 keeps all keys
     std::vector<long long> state_shape;     // State: a tensor of this shape per live request, zeroed when a request starts
     DType state_dtype = DType::F32;
+    // float32 values per live request that the layer's own parts keep beside the mixer (a shift's last row), whatever
+    // the mixer's kind; zeroed when a request starts.  Set by the model, not by the mixer.
+    long long layer_state_floats = 0;
+    bool same_pages(const CacheNeed& o) const {
+        return kind == o.kind && num_kv_heads == o.num_kv_heads && head_dim == o.head_dim && planes == o.planes && window == o.window;
+    }
     bool operator==(const CacheNeed& o) const {
-        return kind == o.kind && num_kv_heads == o.num_kv_heads && head_dim == o.head_dim && planes == o.planes && window == o.window &&
-               state_shape == o.state_shape && state_dtype == o.state_dtype;
+        return same_pages(o) && state_shape == o.state_shape && state_dtype == o.state_dtype && layer_state_floats == o.layer_state_floats;
     }
     static CacheNeed paged(int kv_heads, int head_dim, long long window) {
         CacheNeed n;
@@ -54,6 +59,12 @@ struct CacheNeed {
     // one row of `width` values per token, shared by all heads
     static CacheNeed paged_rows(int width, long long window) {
         CacheNeed n = paged(1, width, window);
+        n.planes = 1;
+        return n;
+    }
+    // one row (key | value) per token and KV head: keys and values of different sizes side by side
+    static CacheNeed paged_joint(int kv_heads, int key_dim, int value_dim, long long window) {
+        CacheNeed n = paged(kv_heads, key_dim + value_dim, window);
         n.planes = 1;
         return n;
     }
@@ -122,6 +133,8 @@ struct CacheView {
     int num_pages = 0, page_size = 0;
     void* state = nullptr;              // [max_slots, state elements] for a mixer with fixed-size state
     size_t state_bytes_per_slot = 0;
+    float* layer_state = nullptr;       // [max_slots, layer_state_floats]: what the layer's own parts keep per request
+    long long layer_state_floats = 0;
     bool writes = true;                 // false: read another entry's cache, store nothing
 };
 
@@ -157,6 +170,7 @@ public:
 struct HalfRotation {
     const float* inv_freq = nullptr;    // float32 [rotary_dim / 2] on the device
     int rotary_dim = 0;
+    float magnitude = 1.0f;             // factor on cos and sin (a rotation with scaled frequencies may have one)
     std::string key;                    // equal keys mean equal tables: consumers may share what they derive from one
 };
 
@@ -188,7 +202,25 @@ public:
                               DType /*dtype_b*/, const Norm* /*second*/, void* /*out*/, void* /*out2*/, DType /*out_dtype*/, int /*num_rows*/) const {
         return false;
     }
+    // residual[t] += this norm of y[t] (a branch's output joins the stream through its norm), in one kernel; false: this
+    // norm cannot (the caller norms into a buffer and adds)
+    virtual bool add_normed(const StepContext& /*ctx*/, float* /*residual*/, const void* /*y*/, DType /*y_dtype*/, int /*num_rows*/) const { return false; }
     virtual int size() const = 0;
+};
+
+// A mix of every token's row with the row of the token in front of it in its request, between a norm and the part that
+// reads it.  Per request it keeps `state_floats()` float32 values (the last row of earlier steps; zeros at the start).
+class Shift : public Part {
+public:
+    using Part::Part;
+    virtual long long state_floats() const = 0;
+    // rows float32 [T, size] (normed) -> out [T, size] in out_dtype; state [slots, slot_floats], this part's values first
+    virtual void forward(const StepContext& ctx, const float* rows, float* state, long long slot_floats, void* out, DType out_dtype) const = 0;
+    // the same with the norm in front (a plain RMSNorm: gain, eps) done here from the float32 stream; false: cannot
+    virtual bool forward_rms(const StepContext& /*ctx*/, const float* /*residual*/, const float* /*gain*/, float /*eps*/, float* /*state*/,
+                             long long /*slot_floats*/, void* /*out*/, DType /*out_dtype*/) const {
+        return false;
+    }
 };
 
 // Something added to the residual stream between layers (before a pass of a repeated run of layers, say).
@@ -435,6 +467,7 @@ struct PartRegistry {
     std::map<std::string, Factory<Embedding>> embeddings;
     std::map<std::string, Factory<Head>> heads;
     std::map<std::string, Factory<StreamAdd>> stream_adds;
+    std::map<std::string, Factory<Shift>> shifts;
 
     static PartRegistry& instance() {
         static PartRegistry r;

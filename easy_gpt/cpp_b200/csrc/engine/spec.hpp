@@ -90,12 +90,15 @@ struct PartSpec {
 //   norm present, placement "post":  x = norm(x + f(x))
 //   no norm:                         x = x + f(x)
 //   output_norm present as well:     x = x + output_norm(f(norm(x)))
+//   shift present (norm "pre"):      x = x + [output_norm] f(shift(norm(x))): the part reads a mix of every token's normed
+//                                    row and the row of the token in front of it (a part of role "shift", with state per request)
 struct SubLayerSpec {
     std::string role;                   // "mixer" or "feed_forward"
     PartSpec part;
     PartSpec norm = PartSpec::none();
     std::string norm_placement = "pre";
     PartSpec output_norm = PartSpec::none();
+    PartSpec shift = PartSpec::none();
 };
 
 struct LayerSpec {
@@ -171,6 +174,8 @@ struct ModelSpec {
                 if (s.role != "mixer" && s.role != "feed_forward") throw std::invalid_argument("a sub-layer's role is 'mixer' or 'feed_forward', not '" + s.role + "'");
                 if (s.norm_placement != "pre" && s.norm_placement != "post") throw std::invalid_argument("norm_placement is 'pre' or 'post'");
                 mixers += s.role == "mixer";
+                if (s.shift.present && (l.parallel || s.role != "mixer" || s.norm_placement != "pre"))
+                    throw std::invalid_argument("a shift stands in front of a mixer, behind a norm in front of it, in a layer that is not parallel");
                 if (l.parallel && (!s.norm.present || s.norm_placement != "pre" || s.output_norm.present))
                     throw std::invalid_argument("a parallel layer's sub-layers each have a norm in front and none behind");
             }

@@ -71,7 +71,7 @@ public:
             if (need.kind == CacheNeed::PagedKV) {
                 Group* g = nullptr;
                 for (auto& have : groups)
-                    if (have->need == need) g = have.get();
+                    if (have->need.same_pages(need)) g = have.get();
                 if (!g) {
                     groups.emplace_back(new Group());
                     g = groups.back().get();
@@ -91,6 +91,12 @@ public:
                 st.memory.allocate(st.bytes_per_slot * (size_t)(max_slots + 1), true);     // one slot more: the scratch slot of padding rows
                 states.emplace(kv.first, std::move(st));
             }
+            if (need.layer_state_floats > 0) {
+                State st;
+                st.bytes_per_slot = (size_t)need.layer_state_floats * 4;
+                st.memory.allocate(st.bytes_per_slot * (size_t)(max_slots + 1), true);
+                layer_states.emplace(kv.first, std::move(st));
+            }
         }
         for (auto& g : groups) g->kv.allocate(g->layer_elems * g->cache_ids.size() * dtype_size(dtype), true);
         fresh_.resize(max_slots);
@@ -99,6 +105,11 @@ public:
     CacheView view(int cache_id, bool writes) const {
         CacheView v;
         v.writes = writes;
+        auto ls = layer_states.find(cache_id);
+        if (ls != layer_states.end()) {
+            v.layer_state = ls->second.memory.as<float>();
+            v.layer_state_floats = (long long)(ls->second.bytes_per_slot / 4);
+        }
         auto it = group_of_cache.find(cache_id);
         if (it != group_of_cache.end()) {
             const Group& g = *groups[it->second];
@@ -126,10 +137,10 @@ public:
     // function calls it before every forward pass, captured or not.
     void zero_fresh_state(cudaStream_t stream) {
         const int n = core.take_fresh_slots(fresh_.data(), max_slots);
-        if (states.empty()) return;
         for (int i = 0; i < n; ++i)
-            for (auto& kv : states)
-                EG_CUDA(cudaMemsetAsync(kv.second.memory.as<char>() + (size_t)fresh_[i] * kv.second.bytes_per_slot, 0, kv.second.bytes_per_slot, stream));
+            for (auto* table : {&states, &layer_states})
+                for (auto& kv : *table)
+                    EG_CUDA(cudaMemsetAsync(kv.second.memory.as<char>() + (size_t)fresh_[i] * kv.second.bytes_per_slot, 0, kv.second.bytes_per_slot, stream));
     }
     size_t kv_bytes_per_token() const {
         size_t total = 0;
@@ -143,6 +154,7 @@ public:
     std::vector<std::unique_ptr<Group>> groups;
     std::map<int, int> group_of_cache;
     std::map<int, State> states;
+    std::map<int, State> layer_states;     // what a layer's own parts keep per request beside the mixer's cache or state
 
 private:
     std::vector<int> fresh_;

@@ -187,7 +187,7 @@ struct TensorRequest {
     std::string name;
     std::vector<std::vector<long long>> shapes;
     bool optional = false;
-    // what random-weights mode draws for it: "" a normal value, "one" / "zero" a constant, "log_decay" the logarithm of a
+    // what random-weights mode draws for it: "" a normal value, "one" / "zero" / "half" a constant, "log_decay" the logarithm of a
     // decay rate between 1 and 16, "step_bias" the inverse softplus of a step size between 1e-3 and 1e-1
     std::string init;
     TensorRequest with_init(const char* how) const {

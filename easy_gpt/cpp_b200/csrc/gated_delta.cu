@@ -1,0 +1,224 @@
+// The gated delta rule: per head a matrix S [dk, dv] (float32, in the request's state slot) that every token lets decay,
+// corrects towards its value along its key, and reads with its query:
+//
+//   q^ = q / sqrt(|q|^2 + unit_eps) * dk^(-1/2),  k^ = k / sqrt(|k|^2 + unit_eps)          (per key head, float32)
+//   beta = sigmoid(b),  g = exp(-exp(A_log) * softplus(a + dt_bias))                          (per head, float32)
+//   S <- g S;  u = beta (v - S^T k^);  S <- S + k^ u^T;  o = S^T q^
+//   y = o / sqrt(mean(o^2) + eps) * w * silu(z)                                               (per head over dv)
+//
+// q, k, v are the convolved and activated projections (float32 [tokens, ...]), b, a and z columns of the projection's
+// float32 output.  Head h reads key head h / (heads / kv_heads).
+//
+// One block per (head, batch entry).  Column j of S belongs to P neighbouring lanes, each with R = ceil(dk / P) of its
+// rows in registers for the entry's whole run of tokens, so a token costs two dot products over the old S (with k^ and
+// with q^, independent of each other: o = g S_old^T q^ + u (k^ . q^)), a few shuffles and one update per element.  The
+// block walks the entry in tiles of tokens staged in shared memory, where it also norms the tile's queries and keys;
+// the tile's outputs are normed per head and gated before they leave.  The slot keeps S as [head, dv, dk], so that a
+// thread's rows are neighbours in memory.  The order of every sum depends on the sizes alone.
+#include "common.cuh"
+
+namespace {
+
+__device__ __forceinline__ float silu_f(float v) { return v / (1.0f + expf(-v)); }
+__device__ __forceinline__ float softplus_f(float v) { return v > 20.0f ? v : log1pf(expf(v)); }
+
+// exp(x) for x <= 0, with the last addition the only rounding that counts: a state that decays slowly is multiplied by
+// thousands of such factors in a row, and an error with a sign of its own would add up over a long sequence.
+__device__ __forceinline__ float decay_exp(float x) {
+    if (x < -104.0f) return 0.0f;
+    const float k = rintf(x * 1.442695041f);
+    float r = fmaf(k, -0.693145751953125f, x);
+    r = fmaf(k, -1.428606765330187e-06f, r);
+    float p = 1.9875691500e-4f;
+    p = fmaf(p, r, 1.3981999507e-3f);
+    p = fmaf(p, r, 8.3334519073e-3f);
+    p = fmaf(p, r, 4.1665795894e-2f);
+    p = fmaf(p, r, 1.6666665459e-1f);
+    p = fmaf(p, r, 5.0000001201e-1f);
+    const float e = 1.0f + fmaf(r * r, p, r);
+    const int ki = (int)k;
+    if (ki >= -125) return __int_as_float(__float_as_int(e) + (ki << 23));
+    return __int_as_float(__float_as_int(e) + ((ki + 100) << 23)) * 7.888609052210118e-31f;
+}
+
+constexpr int TILE = 16;        // tokens staged at a time
+
+template <typename TO, int R, int P>
+__global__ void __launch_bounds__(1024) gated_delta_kernel(const float* __restrict__ qkv, long long ldq, int q_col, int k_col, int v_col,
+                                                           const float* __restrict__ proj, long long ldp, int b_col, int a_col, int z_col,
+                                                           const float* __restrict__ a_log, const float* __restrict__ dt_bias,
+                                                           const float* __restrict__ norm_w, float* __restrict__ state, long long slot_floats,
+                                                           long long state_offset, const int* __restrict__ seq_starts,
+                                                           const int* __restrict__ seq_slots, TO* __restrict__ y, long long ldy, int heads,
+                                                           int kv_heads, int dk, int dv, float unit_eps, float eps) {
+    extern __shared__ float smem[];
+    const int dkp = R * P;                          // dk padded: rows beyond dk see zero keys and queries and stay zero
+    float* s_k = smem;                              // [TILE, dkp]
+    float* s_q = s_k + TILE * dkp;                  // [TILE, dkp]
+    float* s_v = s_q + TILE * dkp;                  // [TILE, dv]
+    float* s_o = s_v + TILE * dv;                   // [TILE, dv]
+    float* s_beta = s_o + TILE * dv;                // [TILE]
+    float* s_g = s_beta + TILE;
+    float* s_kq = s_g + TILE;
+    const int head = blockIdx.x, seq = blockIdx.y;
+    const int kvh = head / (heads / kv_heads);
+    const int start = seq_starts[seq], count = seq_starts[seq + 1] - start;
+    const int j = threadIdx.x / P, part = threadIdx.x % P;
+    const bool active = j < dv;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+    float* S = state + (size_t)seq_slots[seq] * slot_floats + state_offset + ((size_t)head * dv + (active ? j : 0)) * dk;
+    float s[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        const int row = part * R + r;
+        s[r] = (active && row < dk) ? S[row] : 0.f;
+    }
+    const float rate = -expf(a_log[head]), bias = dt_bias[head], q_scale = 1.0f / sqrtf((float)dk);
+    for (int t0 = 0; t0 < count; t0 += TILE) {
+        const int n = min(TILE, count - t0);
+        __syncthreads();                            // the tile before is done with shared memory
+        for (int i = threadIdx.x; i < n * dkp; i += blockDim.x) {
+            const int t = i / dkp, d = i % dkp;
+            const float* row = qkv + (size_t)(start + t0 + t) * ldq;
+            s_k[i] = d < dk ? row[k_col + kvh * dk + d] : 0.f;
+            s_q[i] = d < dk ? row[q_col + kvh * dk + d] : 0.f;
+        }
+        for (int i = threadIdx.x; i < n * dv; i += blockDim.x) {
+            const int t = i / dv, d = i % dv;
+            s_v[i] = qkv[(size_t)(start + t0 + t) * ldq + v_col + head * dv + d];
+        }
+        if (threadIdx.x < n) {
+            const float* row = proj + (size_t)(start + t0 + threadIdx.x) * ldp;
+            s_beta[threadIdx.x] = 1.0f / (1.0f + expf(-row[b_col + head]));
+            s_g[threadIdx.x] = decay_exp(rate * softplus_f(row[a_col + head] + bias));
+        }
+        __syncthreads();
+        // unit keys and queries, and k^ . q^, a warp per token
+        for (int t = warp; t < n; t += warps) {
+            float kk = 0.f, qq = 0.f, kq = 0.f;
+            for (int d = lane; d < dkp; d += 32) {
+                const float a = s_k[t * dkp + d], b = s_q[t * dkp + d];
+                kk = fmaf(a, a, kk);
+                qq = fmaf(b, b, qq);
+                kq = fmaf(a, b, kq);
+            }
+            kk = warp_sum(kk);
+            qq = warp_sum(qq);
+            kq = warp_sum(kq);
+            const float ik = 1.0f / sqrtf(kk + unit_eps), iq = q_scale / sqrtf(qq + unit_eps);
+            for (int d = lane; d < dkp; d += 32) {
+                s_k[t * dkp + d] *= ik;
+                s_q[t * dkp + d] *= iq;
+            }
+            if (lane == 0) s_kq[t] = kq * ik * iq;
+        }
+        __syncthreads();
+        for (int t = 0; t < n; ++t) {
+            const float* kt = s_k + t * dkp + part * R;
+            const float* qt = s_q + t * dkp + part * R;
+            float sk = 0.f, sq = 0.f;
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                sk = fmaf(s[r], kt[r], sk);
+                sq = fmaf(s[r], qt[r], sq);
+            }
+#pragma unroll
+            for (int o = 1; o < P; o <<= 1) {
+                sk += __shfl_xor_sync(0xffffffffu, sk, o);
+                sq += __shfl_xor_sync(0xffffffffu, sq, o);
+            }
+            const float g = s_g[t];
+            const float u = s_beta[t] * ((active ? s_v[t * dv + j] : 0.f) - g * sk);
+#pragma unroll
+            for (int r = 0; r < R; ++r) s[r] = fmaf(kt[r], u, g * s[r]);
+            if (active && part == 0) s_o[t * dv + j] = fmaf(g, sq, u * s_kq[t]);
+        }
+        __syncthreads();
+        // y = o / rms(o) * w * silu(z), a warp per token
+        for (int t = warp; t < n; t += warps) {
+            float ss = 0.f;
+            for (int d = lane; d < dv; d += 32) ss = fmaf(s_o[t * dv + d], s_o[t * dv + d], ss);
+            ss = warp_sum(ss);
+            const float inv = 1.0f / sqrtf(ss / (float)dv + eps);
+            const float* z = proj + (size_t)(start + t0 + t) * ldp + z_col + head * dv;
+            TO* out = y + (size_t)(start + t0 + t) * ldy + head * dv;
+            for (int d = lane; d < dv; d += 32) out[d] = from_f32<TO>(s_o[t * dv + d] * inv * norm_w[d] * silu_f(z[d]));
+        }
+    }
+    if (active) {
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            const int row = part * R + r;
+            if (row < dk) S[row] = s[r];
+        }
+    }
+}
+
+template <typename TO, int R, int P>
+int launch_delta(cudaStream_t stream, const float* qkv, long long ldq, int q_col, int k_col, int v_col, const float* proj, long long ldp, int b_col,
+                 int a_col, int z_col, const float* a_log, const float* dt_bias, const float* norm_w, float* state, long long slot_floats,
+                 long long state_offset, const int* seq_starts, const int* seq_slots, void* y, long long ldy, int num_seqs, int heads, int kv_heads, int dk,
+                 int dv, float unit_eps, float eps) {
+    const int threads = (dv * P + 31) / 32 * 32;
+    const size_t smem = ((size_t)TILE * (2 * R * P + 2 * dv) + 3 * TILE) * sizeof(float);
+    if (threads > 1024 || smem > 200 * 1024) return (int)cudaErrorInvalidValue;
+    auto kernel = gated_delta_kernel<TO, R, P>;
+    if (smem > 48 * 1024) {
+        const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+    }
+    kernel<<<dim3(heads, num_seqs), threads, smem, stream>>>(qkv, ldq, q_col, k_col, v_col, proj, ldp, b_col, a_col, z_col, a_log, dt_bias, norm_w, state,
+                                                             slot_floats, state_offset, seq_starts, seq_slots, (TO*)y, ldy, heads, kv_heads, dk, dv, unit_eps,
+                                                             eps);
+    return eg_launch_status();
+}
+
+template <typename TO>
+int dispatch_delta(int R, int P, cudaStream_t stream, const float* qkv, long long ldq, int q_col, int k_col, int v_col, const float* proj, long long ldp,
+                   int b_col, int a_col, int z_col, const float* a_log, const float* dt_bias, const float* norm_w, float* state, long long slot_floats,
+                   long long state_offset, const int* seq_starts, const int* seq_slots, void* y, long long ldy, int num_seqs, int heads, int kv_heads, int dk,
+                   int dv, float unit_eps, float eps) {
+#define EG_DELTA(RR, PP)                                                                                                                                  \
+    if (R == RR && P == PP)                                                                                                                               \
+        return launch_delta<TO, RR, PP>(stream, qkv, ldq, q_col, k_col, v_col, proj, ldp, b_col, a_col, z_col, a_log, dt_bias, norm_w, state, slot_floats, \
+                                        state_offset, seq_starts, seq_slots, y, ldy, num_seqs, heads, kv_heads, dk, dv, unit_eps, eps)
+    EG_DELTA(4, 4);
+    EG_DELTA(8, 4);
+    EG_DELTA(16, 4);
+    EG_DELTA(16, 8);
+    EG_DELTA(32, 8);
+#undef EG_DELTA
+    return (int)cudaErrorInvalidValue;
+}
+}  // namespace
+
+// How a head's rows are spread for these sizes: P lanes a column with R rows each (R * P >= dk); 0 if the kernel does
+// not take the sizes (a block holds a whole head: dv * P threads, at most 1024).
+EG_API int eg_gated_delta_plan(int dk, int dv, int* rows_per_lane, int* lanes) {
+    if (dk <= 0 || dv <= 0 || dk > 256) return 0;
+    const int P = dk > 64 ? 8 : 4;
+    if (dv * P > 1024) return 0;
+    int R = P == 8 ? 16 : 4;
+    while (R * P < dk) R *= 2;
+    *rows_per_lane = R;
+    *lanes = P;
+    return 1;
+}
+
+// qkv float32 [tokens, ldq]: convolved, activated queries (key heads x dk at q_col), keys (k_col) and values (heads x dv at
+// v_col).  proj float32 [tokens, ldp]: the projection's output with b (heads) at b_col, a (heads) at a_col and the output
+// gate z (heads x dv) at z_col.  state: the requests' slots; S of a request lies state_offset floats into its slot, as
+// [heads, dv, dk].  y [tokens, ldy] in y_dtype.
+EG_API int eg_gated_delta(cudaStream_t stream, const float* qkv, long long ldq, int q_col, int k_col, int v_col, const float* proj, long long ldp,
+                          int b_col, int a_col, int z_col, const float* a_log, const float* dt_bias, const float* norm_w, float* state,
+                          long long slot_floats, long long state_offset, const int* seq_starts, const int* seq_slots, void* y, int y_dtype, long long ldy,
+                          int num_seqs, int heads, int kv_heads, int dk, int dv, float unit_eps, float eps) {
+    if (num_seqs <= 0) return 0;
+    int R = 0, P = 0;
+    if (kv_heads <= 0 || heads % kv_heads || !eg_gated_delta_plan(dk, dv, &R, &P)) return (int)cudaErrorInvalidValue;
+    if (y_dtype == EG_BF16)
+        return dispatch_delta<bf16>(R, P, stream, qkv, ldq, q_col, k_col, v_col, proj, ldp, b_col, a_col, z_col, a_log, dt_bias, norm_w, state, slot_floats,
+                                    state_offset, seq_starts, seq_slots, y, ldy, num_seqs, heads, kv_heads, dk, dv, unit_eps, eps);
+    return dispatch_delta<float>(R, P, stream, qkv, ldq, q_col, k_col, v_col, proj, ldp, b_col, a_col, z_col, a_log, dt_bias, norm_w, state, slot_floats,
+                                 state_offset, seq_starts, seq_slots, y, ldy, num_seqs, heads, kv_heads, dk, dv, unit_eps, eps);
+}

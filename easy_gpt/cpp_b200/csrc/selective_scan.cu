@@ -58,7 +58,7 @@ __global__ void conv_silu_kernel(const T* __restrict__ x, long long ldx, const f
     const int t = (int)(i / channels), c = (int)(i % channels);
     const int seq = token_seq[t], start = seq_starts[seq];
     const float* past = state + (size_t)seq_slots[seq] * slot_floats;
-    float acc = cb[c];
+    float acc = cb ? cb[c] : 0.0f;                          // a convolution without bias hands none
     for (int j = 0; j < taps; ++j) {
         const int src = t - (taps - 1) + j;
         // before the entry's first token: the request's earlier inputs, the newest of which is row taps-2 of the slot
