@@ -77,7 +77,17 @@ struct Params {
     unsigned long long* trace;    // optional: [2] earliest start / latest end of this launch's CTAs (%globaltimer, ns)
     const int* token_list;        // optional: the tokens this launch works on (blockIdx.x indexes it); null: all, in order
     int cluster_merge;            // the splits of a (token, KV head) are one cluster and are merged in its first CTA's shared memory
+    float sink2 = -INFINITY;      // a sink's logit times log2(e): one more term of the softmax's denominator; -inf: none
 };
+
+// acc * this = the softmax's output, with (m, l) the reference (base 2) and sum of the weights that acc holds, and the
+// sink's term 2^(sink2 - m) joining the sum (in a form that cannot overflow whatever m is)
+__device__ __forceinline__ float norm_with_sink(float m, float l, float sink2) {
+    if (!(l > 0.f)) return 0.f;
+    if (sink2 == -INFINITY) return 1.0f / l;
+    const float top = fmaxf(m, sink2), c = exp2f(m - top);
+    return c / fmaf(l, c, exp2f(sink2 - top));
+}
 
 template <int HD, bool DEEP, int TPI, int KW>
 __global__ void __launch_bounds__(TPI * THREADS) attention_paged_kernel(const Params p) {
@@ -358,7 +368,8 @@ __global__ void __launch_bounds__(TPI * THREADS) attention_paged_kernel(const Pa
         }
         const int h = kvh * G + g0 + r;
         if (p.splits == 1) {
-            p.out[(size_t)t * p.ldo + (size_t)h * HD + d] = __float2bfloat16_rn(l > 0.f ? a / l : 0.f);
+            p.out[(size_t)t * p.ldo + (size_t)h * HD + d] =
+                __float2bfloat16_rn(p.sink2 == -INFINITY ? (l > 0.f ? a / l : 0.f) : a * norm_with_sink(m, l, p.sink2));
         } else if (p.cluster_merge) {
             const uint32_t at = incoming + (uint32_t)((cluster_rank * rows + r) * (HD + 2)) * 4u;
             asm volatile("st.shared::cluster.f32 [%0], %1;\n" ::"r"(at + (uint32_t)d * 4u), "f"(a) : "memory");
@@ -398,7 +409,7 @@ __global__ void __launch_bounds__(TPI * THREADS) attention_paged_kernel(const Pa
                 const float2 lo = *reinterpret_cast<const float2*>(part + dq * 4), hi = *reinterpret_cast<const float2*>(part + dq * 4 + 2);
                 a.x += lo.x * w; a.y += lo.y * w; a.z += hi.x * w; a.w += hi.y * w;
             }
-            const float il = l > 0.f ? 1.0f / l : 0.f;
+            const float il = norm_with_sink(m, l, p.sink2);
             const int h = kvh * G + g0 + r;
             *reinterpret_cast<uint2*>(p.out + (size_t)t * p.ldo + (size_t)h * HD + dq * 4) =
                 make_uint2(pack_bf16(a.x * il, a.y * il), pack_bf16(a.z * il, a.w * il));
@@ -455,7 +466,7 @@ __global__ void __launch_bounds__(TPI * THREADS) attention_paged_kernel(const Pa
                     f[s2] = w;
                     l += lp[s2] * w;
                 }
-                inv_l[threadIdx.x] = l > 0.f ? 1.0f / l : 0.f;
+                inv_l[threadIdx.x] = norm_with_sink(m, l, p.sink2);
             }
             __syncthreads();
         }
@@ -619,6 +630,7 @@ struct PrefillParams {
     int num_heads, num_kv_heads, page_size, num_pages, window;
     float scale;
     int* status;
+    float sink2 = -INFINITY;      // as in Params
 };
 
 template <int HD>
@@ -821,7 +833,7 @@ __global__ void __launch_bounds__(THREADS, HD <= 64 ? 4 : 2) attention_prefill_k
     l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
-    const float i0 = l0 > 0.f ? 1.0f / l0 : 0.f, i1 = l1 > 0.f ? 1.0f / l1 : 0.f;
+    const float i0 = norm_with_sink(m0, l0, p.sink2), i1 = norm_with_sink(m1, l1, p.sink2);
 #pragma unroll
     for (int i = 0; i < HD / 8; ++i) {
         const int d = i * 8 + 2 * tig;
@@ -853,12 +865,12 @@ int launch_prefill(cudaStream_t stream, const PrefillParams& p, int num_tiles) {
 // number of keys that were in the cache before this step; those may be fetched before the kernel in front has finished.
 // token_list (may be null): `tokens` indices of the tokens to work on (scratch and counters are indexed by token index,
 // so they cover all tokens of the step either way).
-EG_API int eg_attention_paged(cudaStream_t stream, const void* q, int ldq, const void* k_cache, const void* v_cache,
-                              const int* block_table, int table_stride, const int* token_seq, const int* positions,
-                              const int* seq_context, void* out, int ldo, float* partial_acc, float* partial_ml, int tokens, int num_heads,
-                              int num_kv_heads, int head_dim, int page_size, long long page_stride, long long head_stride,
-                              int num_pages, int window, float scale, int splits, int* status, const void* prefetch,
-                              long long prefetch_bytes, int* counters, int use_pdl, unsigned long long* trace, const int* token_list) {
+static int attention_paged_any(cudaStream_t stream, const void* q, int ldq, const void* k_cache, const void* v_cache,
+                               const int* block_table, int table_stride, const int* token_seq, const int* positions,
+                               const int* seq_context, void* out, int ldo, float* partial_acc, float* partial_ml, int tokens, int num_heads,
+                               int num_kv_heads, int head_dim, int page_size, long long page_stride, long long head_stride,
+                               int num_pages, int window, float scale, int splits, int* status, const void* prefetch,
+                               long long prefetch_bytes, int* counters, int use_pdl, unsigned long long* trace, const int* token_list, float sink2) {
     if (tokens <= 0) return 0;
     if (page_size % 16 || num_kv_heads <= 0 || num_heads % num_kv_heads || splits < 1 || tokens > 0x7fffffff ||
         splits > MAX_SPLITS || (splits > 1 && (!partial_acc || !partial_ml || !counters || ldo % 4 || (uintptr_t)out % 8)))
@@ -867,6 +879,7 @@ EG_API int eg_attention_paged(cudaStream_t stream, const void* q, int ldq, const
              table_stride, token_seq, positions, seq_context, (bf16*)out, ldo, partial_acc, partial_ml, num_heads, num_kv_heads,
              page_size, num_pages, window, splits, scale, status, prefetch_bytes >= 16 ? prefetch : nullptr, prefetch_bytes,
              counters, use_pdl, trace, token_list};
+    p.sink2 = sink2;
     switch (head_dim) {
         case 32: return launch<32>(stream, p, tokens);
         case 64: return launch<64>(stream, p, tokens);
@@ -876,22 +889,65 @@ EG_API int eg_attention_paged(cudaStream_t stream, const void* q, int ldq, const
     }
 }
 
+EG_API int eg_attention_paged(cudaStream_t stream, const void* q, int ldq, const void* k_cache, const void* v_cache,
+                              const int* block_table, int table_stride, const int* token_seq, const int* positions,
+                              const int* seq_context, void* out, int ldo, float* partial_acc, float* partial_ml, int tokens, int num_heads,
+                              int num_kv_heads, int head_dim, int page_size, long long page_stride, long long head_stride,
+                              int num_pages, int window, float scale, int splits, int* status, const void* prefetch,
+                              long long prefetch_bytes, int* counters, int use_pdl, unsigned long long* trace, const int* token_list) {
+    return attention_paged_any(stream, q, ldq, k_cache, v_cache, block_table, table_stride, token_seq, positions, seq_context, out, ldo, partial_acc,
+                               partial_ml, tokens, num_heads, num_kv_heads, head_dim, page_size, page_stride, head_stride, num_pages, window, scale, splits,
+                               status, prefetch, prefetch_bytes, counters, use_pdl, trace, token_list, -INFINITY);
+}
+
+// The same with a sink: one more term exp(sink_logit) in every softmax's denominator, which has no value.
+EG_API int eg_attention_paged_sink(cudaStream_t stream, const void* q, int ldq, const void* k_cache, const void* v_cache,
+                                   const int* block_table, int table_stride, const int* token_seq, const int* positions,
+                                   const int* seq_context, void* out, int ldo, float* partial_acc, float* partial_ml, int tokens, int num_heads,
+                                   int num_kv_heads, int head_dim, int page_size, long long page_stride, long long head_stride,
+                                   int num_pages, int window, float scale, int splits, int* status, int* counters, int use_pdl,
+                                   const int* token_list, float sink_logit) {
+    return attention_paged_any(stream, q, ldq, k_cache, v_cache, block_table, table_stride, token_seq, positions, seq_context, out, ldo, partial_acc,
+                               partial_ml, tokens, num_heads, num_kv_heads, head_dim, page_size, page_stride, head_stride, num_pages, window, scale, splits,
+                               status, nullptr, 0, counters, use_pdl, nullptr, token_list, sink_logit * 1.4426950408889634f);
+}
+
 // Prompt portions in tiles of 64 query tokens: tiles[num_tiles][3] = (block table row, first token, count <= 64);
 // the tokens of a tile are consecutive positions of one request.  Head sizes 32, 64, 128; pages of a multiple of 16.
-EG_API int eg_attention_prefill(cudaStream_t stream, const void* q, int ldq, const void* k_cache, const void* v_cache,
-                                const int* block_table, int table_stride, const int* positions, const int* tiles,
-                                int num_tiles, void* out, int ldo, int num_heads, int num_kv_heads, int head_dim,
-                                int page_size, long long page_stride, long long head_stride, int num_pages, int window,
-                                float scale, int* status) {
+static int attention_prefill_any(cudaStream_t stream, const void* q, int ldq, const void* k_cache, const void* v_cache,
+                                 const int* block_table, int table_stride, const int* positions, const int* tiles,
+                                 int num_tiles, void* out, int ldo, int num_heads, int num_kv_heads, int head_dim,
+                                 int page_size, long long page_stride, long long head_stride, int num_pages, int window,
+                                 float scale, int* status, float sink2) {
     if (num_tiles <= 0) return 0;
     if (page_size % 16 || num_kv_heads <= 0 || num_heads % num_kv_heads || num_heads > 65535) return (int)cudaErrorInvalidValue;
     PrefillParams p{(const bf16*)q, ldq, (const bf16*)k_cache, (const bf16*)v_cache, page_stride, head_stride, block_table,
                     table_stride, positions, tiles, (bf16*)out, ldo, num_heads, num_kv_heads, page_size, num_pages, window,
                     scale, status};
+    p.sink2 = sink2;
     switch (head_dim) {
         case 32: return launch_prefill<32>(stream, p, num_tiles);
         case 64: return launch_prefill<64>(stream, p, num_tiles);
         case 128: return launch_prefill<128>(stream, p, num_tiles);
         default: return (int)cudaErrorInvalidValue;
     }
+}
+
+EG_API int eg_attention_prefill(cudaStream_t stream, const void* q, int ldq, const void* k_cache, const void* v_cache,
+                                const int* block_table, int table_stride, const int* positions, const int* tiles,
+                                int num_tiles, void* out, int ldo, int num_heads, int num_kv_heads, int head_dim,
+                                int page_size, long long page_stride, long long head_stride, int num_pages, int window,
+                                float scale, int* status) {
+    return attention_prefill_any(stream, q, ldq, k_cache, v_cache, block_table, table_stride, positions, tiles, num_tiles, out, ldo, num_heads, num_kv_heads,
+                                 head_dim, page_size, page_stride, head_stride, num_pages, window, scale, status, -INFINITY);
+}
+
+// The same with a sink: one more term exp(sink_logit) in every softmax's denominator, which has no value.
+EG_API int eg_attention_prefill_sink(cudaStream_t stream, const void* q, int ldq, const void* k_cache, const void* v_cache,
+                                     const int* block_table, int table_stride, const int* positions, const int* tiles,
+                                     int num_tiles, void* out, int ldo, int num_heads, int num_kv_heads, int head_dim,
+                                     int page_size, long long page_stride, long long head_stride, int num_pages, int window,
+                                     float scale, int* status, float sink_logit) {
+    return attention_prefill_any(stream, q, ldq, k_cache, v_cache, block_table, table_stride, positions, tiles, num_tiles, out, ldo, num_heads, num_kv_heads,
+                                 head_dim, page_size, page_stride, head_stride, num_pages, window, scale, status, sink_logit * 1.4426950408889634f);
 }

@@ -1,6 +1,8 @@
-// Grouped-query attention whose keys and values have sizes of their own, over a paged cache that keeps one row
-// (key | value) per token and KV head: preparation of queries, keys and values, and the attention itself for the
-// 32-bit path and for sizes the tensor-core kernel (attention_sink_mma.cu) does not take.
+// Grouped-query attention whose keys and values have sizes of their own, over a paged cache that keeps either one row
+// (key | value) per token and KV head or, where the two sizes are equal, keys and values in planes of their own (the
+// layout the tensor-core kernels read): preparation of queries, keys and values, and the attention itself for the 32-bit
+// path and for sizes the tensor-core kernels do not take.  A key lies at k[page * page_stride + head * head_stride +
+// offset * row_stride], its value at the same place from v.
 //
 // Preparation, per token at position p (float32 throughout, from the float32 output of the projections):
 //   the first rot_dims values of every query and key head are turned in pairs (i, i + rot_dims/2) by the angle
@@ -22,7 +24,8 @@ constexpr int MAX_PER_LANE = 8;      // value size <= 256
 // one warp per (token, head): heads 0..H-1 are queries, H..H+G-1 keys (each with its value row)
 template <typename T>
 __global__ void __launch_bounds__(128) sink_prepare_kernel(const float* __restrict__ proj, long long ld, const float2* __restrict__ table, int half,
-                                                           float magnitude, const int* __restrict__ slot_map, T* __restrict__ cache, int page_size,
+                                                           float magnitude, const int* __restrict__ slot_map, T* __restrict__ k_cache,
+                                                           T* __restrict__ v_cache, int row_stride, long long head_stride, int page_size,
                                                            long long page_stride, long long pool_slots, T* __restrict__ q_out, int tokens, int heads,
                                                            int kv_heads, int dk, int dv, float unit_eps, int* status) {
     const int lane = threadIdx.x & 31;
@@ -35,16 +38,17 @@ __global__ void __launch_bounds__(128) sink_prepare_kernel(const float* __restri
     if (is_q) {
         dst = q_out + ((size_t)t * heads + h) * dk;
     } else {
-        if (!cache) return;
+        if (!k_cache) return;
         const long long slot = slot_map[t];
         if (slot < 0 || slot >= pool_slots) {
             if (lane == 0) atomicOr(status, EG_STATUS_BAD_SLOT);
             return;
         }
         const int g = h - heads;
-        dst = cache + (slot / page_size) * page_stride + ((long long)g * page_size + slot % page_size) * (dk + dv);
+        const long long at = (slot / page_size) * page_stride + g * head_stride + (slot % page_size) * (long long)row_stride;
+        dst = k_cache + at;
         const float* v = proj + (size_t)t * ld + (size_t)(heads + kv_heads) * dk + (size_t)g * dv;
-        for (int d = lane; d < dv; d += 32) dst[dk + d] = from_f32<T>(v[d]);
+        for (int d = lane; d < dv; d += 32) v_cache[at + d] = from_f32<T>(v[d]);
     }
     const int rot = 2 * half;
     float ss = 0.f;
@@ -74,7 +78,8 @@ __global__ void __launch_bounds__(128) sink_prepare_kernel(const float* __restri
 
 template <typename T>
 __global__ void __launch_bounds__(WARPS * 32)
-sink_attention_kernel(const T* __restrict__ q, const T* __restrict__ cache, const int* __restrict__ block_table, int table_stride,
+sink_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T* __restrict__ v_cache, int row_stride, long long head_stride,
+                      const int* __restrict__ block_table, int table_stride,
                       const int* __restrict__ token_seq, const int* __restrict__ positions, const int* __restrict__ token_list, T* __restrict__ out,
                       long long ldo, int heads, int kv_heads, int dk, int dv, int page_size, long long page_stride, int num_pages, int window,
                       float scale, int has_sink, float sink_logit, int* status) {
@@ -86,7 +91,6 @@ sink_attention_kernel(const T* __restrict__ q, const T* __restrict__ cache, cons
     const int g = h / (heads / kv_heads);
     const int pos = positions[t];
     const int* table = block_table + (size_t)token_seq[t] * table_stride;
-    const int width = dk + dv;
     float* qs = q_shared + warp * dk;
     const T* qrow = q + ((size_t)t * heads + h) * dk;
     for (int d = lane; d < dk; d += 32) qs[d] = to_f32<T>(qrow[d]);
@@ -103,11 +107,11 @@ sink_attention_kernel(const T* __restrict__ q, const T* __restrict__ cache, cons
         if (kpos <= pos) {
             const int page = table[kpos / page_size];
             if (page < 0 || page >= num_pages) atomicOr(status, EG_STATUS_BAD_PAGE);
-            else row_off = (long long)page * page_stride + ((long long)g * page_size + kpos % page_size) * width;
+            else row_off = (long long)page * page_stride + g * head_stride + (long long)(kpos % page_size) * row_stride;
         }
         float s = -INFINITY;
         if (row_off >= 0) {
-            const T* krow = cache + row_off;
+            const T* krow = k_cache + row_off;
             float dot = 0.0f;
             for (int d = 0; d < dk; ++d) dot = fmaf(qs[d], to_f32<T>(krow[d]), dot);
             s = dot * scale;
@@ -124,7 +128,7 @@ sink_attention_kernel(const T* __restrict__ q, const T* __restrict__ cache, cons
             const float pj = __shfl_sync(0xffffffffu, p, j);
             const long long off_j = __shfl_sync(0xffffffffu, row_off, j);
             if (off_j < 0) continue;
-            const T* vrow = cache + off_j + dk;
+            const T* vrow = v_cache + off_j;
 #pragma unroll
             for (int i = 0; i < MAX_PER_LANE; ++i) {
                 const int d = lane + 32 * i;
@@ -151,26 +155,28 @@ sink_attention_kernel(const T* __restrict__ q, const T* __restrict__ cache, cons
 }  // namespace
 
 // proj float32 [tokens, ld]: query heads, key heads, value heads side by side.  table: cos/sin [tokens, rot_dims/2, 2] or
-// null with rot_dims 0.  cache null: nothing is stored (the entry reads another entry's cache).  q_out [tokens, heads, dk].
+// null with rot_dims 0.  k_cache null: nothing is stored (the entry reads another entry's cache).  q_out [tokens, heads, dk].
 EG_API int eg_sink_attention_prepare(cudaStream_t stream, int dtype, const float* proj, long long ld, const float* table, int rot_dims, float magnitude,
-                                     const int* slot_map, void* cache, int page_size, long long page_stride, long long pool_slots, void* q_out,
-                                     int tokens, int heads, int kv_heads, int dk, int dv, float unit_eps, int* status) {
+                                     const int* slot_map, void* k_cache, void* v_cache, int row_stride, long long head_stride, int page_size,
+                                     long long page_stride, long long pool_slots, void* q_out, int tokens, int heads, int kv_heads, int dk, int dv,
+                                     float unit_eps, int* status) {
     if (tokens <= 0) return 0;
     if (rot_dims < 0 || rot_dims % 2 || rot_dims > dk || (rot_dims > 0 && !table)) return (int)cudaErrorInvalidValue;
     const long long warps = (long long)tokens * (heads + kv_heads);
     const unsigned blocks = (unsigned)((warps + 3) / 4);
     if (dtype == EG_BF16)
-        sink_prepare_kernel<bf16><<<blocks, 128, 0, stream>>>(proj, ld, (const float2*)table, rot_dims / 2, magnitude, slot_map, (bf16*)cache, page_size,
-                                                              page_stride, pool_slots, (bf16*)q_out, tokens, heads, kv_heads, dk, dv, unit_eps, status);
+        sink_prepare_kernel<bf16><<<blocks, 128, 0, stream>>>(proj, ld, (const float2*)table, rot_dims / 2, magnitude, slot_map, (bf16*)k_cache, (bf16*)v_cache,
+                                                              row_stride, head_stride, page_size, page_stride, pool_slots, (bf16*)q_out, tokens, heads, kv_heads, dk, dv, unit_eps, status);
     else
-        sink_prepare_kernel<float><<<blocks, 128, 0, stream>>>(proj, ld, (const float2*)table, rot_dims / 2, magnitude, slot_map, (float*)cache, page_size,
-                                                               page_stride, pool_slots, (float*)q_out, tokens, heads, kv_heads, dk, dv, unit_eps, status);
+        sink_prepare_kernel<float><<<blocks, 128, 0, stream>>>(proj, ld, (const float2*)table, rot_dims / 2, magnitude, slot_map, (float*)k_cache, (float*)v_cache,
+                                                               row_stride, head_stride, page_size, page_stride, pool_slots, (float*)q_out, tokens, heads, kv_heads, dk, dv, unit_eps, status);
     return eg_launch_status();
 }
 
-// q [tokens, heads, dk]; cache rows (key | value) of dk + dv values; out [tokens, ldo] with head h at column h * dv.
+// q [tokens, heads, dk]; out [tokens, ldo] with head h at column h * dv.
 // token_list: the tokens to work on (num_tokens of them), or null for all.  Returns cudaErrorInvalidValue for sizes it does not take.
-EG_API int eg_sink_attention(cudaStream_t stream, int dtype, const void* q, const void* cache, const int* block_table, int table_stride,
+EG_API int eg_sink_attention(cudaStream_t stream, int dtype, const void* q, const void* k_cache, const void* v_cache, int row_stride, long long head_stride,
+                             const int* block_table, int table_stride,
                              const int* token_seq, const int* positions, const int* token_list, void* out, long long ldo, int num_tokens, int heads,
                              int kv_heads, int dk, int dv, int page_size, long long page_stride, int num_pages, int window, float scale, int has_sink,
                              float sink_logit, int* status) {
@@ -179,12 +185,13 @@ EG_API int eg_sink_attention(cudaStream_t stream, int dtype, const void* q, cons
     dim3 grid(num_tokens, (heads + WARPS - 1) / WARPS);
     const size_t smem = (size_t)WARPS * dk * sizeof(float);
     if (dtype == EG_BF16)
-        sink_attention_kernel<bf16><<<grid, WARPS * 32, smem, stream>>>((const bf16*)q, (const bf16*)cache, block_table, table_stride, token_seq, positions,
+        sink_attention_kernel<bf16><<<grid, WARPS * 32, smem, stream>>>((const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, row_stride, head_stride, block_table,
+                                                                        table_stride, token_seq, positions,
                                                                         token_list, (bf16*)out, ldo, heads, kv_heads, dk, dv, page_size, page_stride,
                                                                         num_pages, window, scale, has_sink, sink_logit, status);
     else
-        sink_attention_kernel<float><<<grid, WARPS * 32, smem, stream>>>((const float*)q, (const float*)cache, block_table, table_stride, token_seq,
-                                                                         positions, token_list, (float*)out, ldo, heads, kv_heads, dk, dv, page_size,
+        sink_attention_kernel<float><<<grid, WARPS * 32, smem, stream>>>((const float*)q, (const float*)k_cache, (const float*)v_cache, row_stride, head_stride, block_table,
+                                                                         table_stride, token_seq, positions, token_list, (float*)out, ldo, heads, kv_heads, dk, dv, page_size,
                                                                          page_stride, num_pages, window, scale, has_sink, sink_logit, status);
     return eg_launch_status();
 }

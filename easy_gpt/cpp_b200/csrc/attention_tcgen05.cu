@@ -217,6 +217,7 @@ struct Params {
     int num_heads, num_kv_heads, page_size, num_pages, window;
     long long page_rows, head_rows;           // in rows of the cache maps: per page, per KV head
     float scale;
+    float sink2 = -INFINITY;       // a sink's logit times log2(e): one more term of the softmax's denominator; -inf: none
     int* status;
     long long* trace;          // optional (profiling): [32][8] clock stamps of the first CTA's first softmax warp, then per unit
                                // [4]: start, end (ns), SM, key tiles
@@ -228,6 +229,15 @@ struct Params {
     int num_tiles, max_parts, part_tiles;
     int piece_rows;            // keys a TMA box of K or V holds: 64, 32 or 16, a divisor of the page size
 };
+
+// acc * this = the softmax's output, with (m, l) the reference (base 2) and sum of the weights that acc holds, and the
+// sink's term 2^(sink2 - m) joining the sum (in a form that cannot overflow whatever m is)
+__device__ __forceinline__ float norm_with_sink(float m, float l, float sink2) {
+    if (!(l > 0.f)) return 0.f;
+    if (sink2 == -INFINITY) return 1.0f / l;
+    const float top = fmaxf(m, sink2), c = exp2f(m - top);
+    return c / fmaf(l, c, exp2f(sink2 - top));
+}
 
 // The 64-bit shared-memory descriptor from its constant high word and a low word (start address, leading offset).
 __device__ __forceinline__ uint64_t desc_from(uint32_t lo, uint32_t hi) {
@@ -640,7 +650,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                 // the second group's rows are with the first
             } else if (ok && parts == 1) {
                 tc_fence_after();
-                const float inv = l > 0.f ? 1.0f / l : 0.f;
+                const float inv = norm_with_sink(m, l, p.sink2);
                 uint4* dst = reinterpret_cast<uint4*>(p.out + (size_t)(t0 + row) * p.ldo + (size_t)h * HD);
 #pragma unroll
                 for (int c0 = 0; c0 < HD; c0 += 32) {
@@ -742,7 +752,7 @@ attention_merge_parts_kernel(const Params p) {
             w[i] = ml[i].x == -INFINITY ? 0.f : exp2f(ml[i].x - big);                     // -inf: that part saw no key of this row
             total += w[i] * ml[i].y;
         }
-        const float inv = total > 0.f ? 1.0f / total : 0.f;
+        const float inv = norm_with_sink(big, total, p.sink2);
         float acc[16];
 #pragma unroll
         for (int e = 0; e < 16; ++e) acc[e] = 0.f;
@@ -803,12 +813,12 @@ EG_API int eg_attention_prefill_groups(int head_dim) { return head_dim == 64 ? 2
 // A query tile's keys are cut into parts of about part_tiles key tiles (of 64), at most max_parts (<= 8): partial_o
 // takes num_tiles * num_heads * max_parts * 128 * head_dim floats, partial_ml * 128 * 2; queue: two zeroed ints
 // (left zero).
-EG_API int eg_attention_prefill_tcgen05(cudaStream_t stream, const void* q, long long ldq, int total_tokens, const void* k_cache,
+static int attention_prefill_tcgen05_any(cudaStream_t stream, const void* q, long long ldq, int total_tokens, const void* k_cache,
                                         const void* v_cache, const int* block_table, int table_stride, const int* positions,
                                         const int* tiles, int num_tiles, void* out, long long ldo, int num_heads, int num_kv_heads,
                                         int head_dim, int page_size, long long page_stride, long long head_stride, int num_pages,
                                         int window, float scale, int* status, long long* trace, int max_parts, int part_tiles, float* partial_o, float* partial_ml,
-                                        int* queue) {
+                                        int* queue, float sink2) {
     if (num_tiles <= 0) return 0;
     if (max_parts < 1 || max_parts > MERGE_MAX_PARTS || part_tiles < 1 || !queue || (max_parts > 1 && (!partial_o || !partial_ml)))
         return (int)cudaErrorInvalidValue;
@@ -833,6 +843,7 @@ EG_API int eg_attention_prefill_tcgen05(cudaStream_t stream, const void* q, long
     p.page_rows = page_stride / head_dim;
     p.head_rows = head_stride / head_dim;
     p.scale = scale;
+    p.sink2 = sink2;
     p.status = status;
     p.trace = trace;
     p.partial_o = partial_o;
@@ -877,4 +888,27 @@ EG_API int eg_attention_prefill_tcgen05(cudaStream_t stream, const void* q, long
     cfg.numAttrs = 1;
     return (int)(head_dim == 64 ? cudaLaunchKernelEx(&cfg, attention_merge_parts_kernel<64>, p)
                                 : cudaLaunchKernelEx(&cfg, attention_merge_parts_kernel<128>, p));
+}
+
+EG_API int eg_attention_prefill_tcgen05(cudaStream_t stream, const void* q, long long ldq, int total_tokens, const void* k_cache,
+                                        const void* v_cache, const int* block_table, int table_stride, const int* positions,
+                                        const int* tiles, int num_tiles, void* out, long long ldo, int num_heads, int num_kv_heads,
+                                        int head_dim, int page_size, long long page_stride, long long head_stride, int num_pages,
+                                        int window, float scale, int* status, long long* trace, int max_parts, int part_tiles, float* partial_o, float* partial_ml,
+                                        int* queue) {
+    return attention_prefill_tcgen05_any(stream, q, ldq, total_tokens, k_cache, v_cache, block_table, table_stride, positions, tiles, num_tiles, out, ldo,
+                                         num_heads, num_kv_heads, head_dim, page_size, page_stride, head_stride, num_pages, window, scale, status, trace,
+                                         max_parts, part_tiles, partial_o, partial_ml, queue, -INFINITY);
+}
+
+// The same with a sink: one more term exp(sink_logit) in every softmax's denominator, which has no value.
+EG_API int eg_attention_prefill_tcgen05_sink(cudaStream_t stream, const void* q, long long ldq, int total_tokens, const void* k_cache,
+                                             const void* v_cache, const int* block_table, int table_stride, const int* positions,
+                                             const int* tiles, int num_tiles, void* out, long long ldo, int num_heads, int num_kv_heads,
+                                             int head_dim, int page_size, long long page_stride, long long head_stride, int num_pages,
+                                             int window, float scale, int* status, int max_parts, int part_tiles, float* partial_o, float* partial_ml,
+                                             int* queue, float sink_logit) {
+    return attention_prefill_tcgen05_any(stream, q, ldq, total_tokens, k_cache, v_cache, block_table, table_stride, positions, tiles, num_tiles, out, ldo,
+                                         num_heads, num_kv_heads, head_dim, page_size, page_stride, head_stride, num_pages, window, scale, status, nullptr,
+                                         max_parts, part_tiles, partial_o, partial_ml, queue, sink_logit * 1.4426950408889634f);
 }

@@ -138,9 +138,15 @@ int eg_embedding_gather_scaled(cudaStream_t stream, int dtype, const int* ids, c
 // sandwich.cu
 int eg_scale_f32(cudaStream_t stream, float* x, long long n, float s);
 // attention_sink.cu
-int eg_sink_attention_prepare(cudaStream_t stream, int dtype, const float* proj, long long ld, const float* table, int rot_dims, float magnitude, const int* slot_map, void* cache, int page_size, long long page_stride, long long pool_slots, void* q_out, int tokens, int heads, int kv_heads, int dk, int dv, float unit_eps, int* status);
+int eg_sink_attention_prepare(cudaStream_t stream, int dtype, const float* proj, long long ld, const float* table, int rot_dims, float magnitude, const int* slot_map, void* k_cache, void* v_cache, int row_stride, long long head_stride, int page_size, long long page_stride, long long pool_slots, void* q_out, int tokens, int heads, int kv_heads, int dk, int dv, float unit_eps, int* status);
 // attention_sink.cu
-int eg_sink_attention(cudaStream_t stream, int dtype, const void* q, const void* cache, const int* block_table, int table_stride, const int* token_seq, const int* positions, const int* token_list, void* out, long long ldo, int num_tokens, int heads, int kv_heads, int dk, int dv, int page_size, long long page_stride, int num_pages, int window, float scale, int has_sink, float sink_logit, int* status);
+int eg_sink_attention(cudaStream_t stream, int dtype, const void* q, const void* k_cache, const void* v_cache, int row_stride, long long head_stride, const int* block_table, int table_stride, const int* token_seq, const int* positions, const int* token_list, void* out, long long ldo, int num_tokens, int heads, int kv_heads, int dk, int dv, int page_size, long long page_stride, int num_pages, int window, float scale, int has_sink, float sink_logit, int* status);
+// attention_paged.cu
+int eg_attention_paged_sink(cudaStream_t stream, const void* q, int ldq, const void* k_cache, const void* v_cache, const int* block_table, int table_stride, const int* token_seq, const int* positions, const int* seq_context, void* out, int ldo, float* partial_acc, float* partial_ml, int tokens, int num_heads, int num_kv_heads, int head_dim, int page_size, long long page_stride, long long head_stride, int num_pages, int window, float scale, int splits, int* status, int* counters, int use_pdl, const int* token_list, float sink_logit);
+// attention_paged.cu
+int eg_attention_prefill_sink(cudaStream_t stream, const void* q, int ldq, const void* k_cache, const void* v_cache, const int* block_table, int table_stride, const int* positions, const int* tiles, int num_tiles, void* out, int ldo, int num_heads, int num_kv_heads, int head_dim, int page_size, long long page_stride, long long head_stride, int num_pages, int window, float scale, int* status, float sink_logit);
+// attention_tcgen05.cu
+int eg_attention_prefill_tcgen05_sink(cudaStream_t stream, const void* q, long long ldq, int total_tokens, const void* k_cache, const void* v_cache, const int* block_table, int table_stride, const int* positions, const int* tiles, int num_tiles, void* out, long long ldo, int num_heads, int num_kv_heads, int head_dim, int page_size, long long page_stride, long long head_stride, int num_pages, int window, float scale, int* status, int max_parts, int part_tiles, float* partial_o, float* partial_ml, int* queue, float sink_logit);
 // gated_delta.cu
 int eg_gated_delta_plan(int dk, int dv, int* rows_per_lane, int* lanes);
 // gated_delta.cu

@@ -48,7 +48,10 @@ private:
 // position encoding (a half rotation over its first dimensions, with the encoding's factor on cos and sin) and then, with
 // unit_eps given, divided by their root mean square per head;  score = (q . k) * scale over the last `window` positions
 // (all, if none is given);  weights = exp(s_j) / (exp(sink_logit) + sum exp(s_i)) if a sink logit is given, else the plain
-// softmax;  out = W_o (heads' values side by side).  The cache keeps one row (key | value) per token and key head.
+// softmax;  out = W_o (heads' values side by side).  The cache keeps one row (key | value) per token and key head; where
+// dim == vdim it keeps keys and values in planes of their own, the layout of the engine's tensor-core attention kernels,
+// which then do the work in bfloat16 (prompt portions on tcgen05 or mma.sync tiles, single tokens split over their keys),
+// with the sink as one more term of their final sums.
 // Parameters: hidden_size, heads, kv_heads, dim, vdim, scale, window, sink_logit, unit_eps.  Tensors: .q .k .v .o.
 class SinkAttention : public Mixer {
 public:
@@ -79,10 +82,14 @@ public:
     }
     size_t weight_bytes() const override { return qkv_.weight_bytes() + out_.weight_bytes(); }
     size_t arena_bytes(long long T) const override {
-        return (size_t)T * ((size_t)qkv_.out_features * 4 + (size_t)heads_ * (dk_ + dv_) * 4 + (size_t)hidden_ * 4) + sink_scratch_bytes() + (1u << 16);
+        // partial results of an attention whose keys are shared by several CTAs: as the engine's attention sizes them
+        const size_t partials = plans::PREFILL_PARTS_SCRATCH_BYTES + (size_t)(4 * plans::sm_count() + 64) * 128 * (size_t)(dv_ + 2) * 4;
+        return (size_t)T * ((size_t)qkv_.out_features * 4 + (size_t)heads_ * (dk_ + dv_) * 4 + (size_t)hidden_ * 4) + (planes() ? partials : 0) + (1u << 16);
     }
     bool capturable() const override { return true; }
-    CacheNeed cache_need() const override { return CacheNeed::paged_joint(kv_heads_, dk_, dv_, window_); }
+    // keys and values in planes of their own where their sizes are equal, else side by side in one row
+    bool planes() const { return dk_ == dv_; }
+    CacheNeed cache_need() const override { return planes() ? CacheNeed::paged(kv_heads_, dk_, window_) : CacheNeed::paged_joint(kv_heads_, dk_, dv_, window_); }
 
     Delta forward(const StepContext& ctx, PartInput in, const CacheView& cache, const FollowingNorm*) override {
         const int T = ctx.num_tokens;
@@ -96,14 +103,49 @@ public:
         if (position && !rotates) throw DeviceError("sink attention takes a half rotation or no position encoding");
         if (rotates && rot.rotary_dim > dk_) throw DeviceError("sink attention: the rotation covers more than a head");
         const float* table = rotates ? step_rotation_table(ctx, rot) : nullptr;
-        void* q = ctx.take_rows(T, heads_ * dk_, dtype);
+        Rows q{ctx.take_rows(T, heads_ * dk_, dtype), dtype, T, heads_ * dk_, heads_ * dk_};
+        // where a key's row lies: planes of their own, or behind one another in a row of dim + vdim values
+        void* values = planes() ? cache.v : (char*)cache.k + (size_t)dk_ * dtype_size(dtype);
+        const int row_stride = planes() ? dk_ : dk_ + dv_;
         launch_check(eg_sink_attention_prepare(ctx.stream, (int)dtype, (const float*)proj.p, proj.ld, table, rotates ? rot.rotary_dim : 0, rot.magnitude,
-                                               tables.slot_map, cache.writes ? cache.k : nullptr, cache.page_size, cache.page_stride,
-                                               (long long)cache.num_pages * cache.page_size, q, T, heads_, kv_heads_, dk_, dv_, unit_eps_, ctx.status),
-                     "sink_attention_prepare");
+                                               tables.slot_map, cache.writes ? cache.k : nullptr, values, row_stride, cache.head_stride, cache.page_size,
+                                               cache.page_stride, (long long)cache.num_pages * cache.page_size, q.p, T, heads_, kv_heads_, dk_, dv_, unit_eps_,
+                                               ctx.status), "sink_attention_prepare");
         Rows attn{ctx.take_rows(T, heads_ * dv_, dtype), dtype, T, heads_ * dv_, heads_ * dv_};
         const int window = window_ < 0 ? 0 : (int)window_;
-        attend(ctx, q, cache, tables, attn, window);
+        const long long longest = window_ < 0 ? ctx.max_context_len : std::min<long long>(ctx.max_context_len, window_ + 255);
+        if (!has_sink_ || !planes() || !plans::attention_paged_takes(dtype, dk_, cache.page_size)) {
+            launch_check(eg_sink_attention(ctx.stream, (int)dtype, q.p, cache.k, values, row_stride, cache.head_stride, tables.block_table, tables.table_width,
+                                           ctx.token_seq, ctx.positions, nullptr, attn.p, attn.ld, T, heads_, kv_heads_, dk_, dv_, cache.page_size,
+                                           cache.page_stride, cache.num_pages, window, scale_, has_sink_ ? 1 : 0, sink_, ctx.status), "sink_attention");
+        } else if (ctx.query_tiles && plans::attention_prefill_takes(dtype, dk_, cache.page_size)) {
+            // prompt portions in tiles of query tokens, on tcgen05 when they are long enough to fill its 128-row tiles
+            if (ctx.max_query_len >= plans::TCGEN05_ATTENTION_MIN_QUERY && plans::attention_prefill_tcgen05_takes(dtype, dk_, cache.page_size)) {
+                int parts, part_tiles;
+                plans::attention_prefill_parts(ctx.num_tiles, heads_, dk_, longest, &parts, &part_tiles);
+                const size_t slots = (size_t)ctx.num_tiles * heads_;
+                while (parts > 1 && slots * parts * 128 * (dk_ + 2) * 4 > plans::PREFILL_PARTS_SCRATCH_BYTES) --parts;
+                float *partial_o = nullptr, *partial_ml = nullptr;
+                if (parts > 1) {
+                    partial_o = ctx.take<float>(slots * parts * 128 * dk_);
+                    partial_ml = ctx.take<float>(slots * parts * 128 * 2);
+                }
+                launch_check(eg_attention_prefill_tcgen05_sink(ctx.stream, q.p, q.ld, T, cache.k, cache.v, tables.block_table, tables.table_width, ctx.positions,
+                                                               ctx.query_tiles, ctx.num_tiles, attn.p, attn.ld, heads_, kv_heads_, dk_, cache.page_size,
+                                                               cache.page_stride, cache.head_stride, cache.num_pages, window, scale_, ctx.status, parts, part_tiles,
+                                                               partial_o, partial_ml, ctx.scratch->prefill_queue.as<int>(), sink_), "attention_prefill_tcgen05_sink");
+            } else {
+                launch_check(eg_attention_prefill_sink(ctx.stream, q.p, (int)q.ld, cache.k, cache.v, tables.block_table, tables.table_width, ctx.positions,
+                                                       ctx.query_tiles, ctx.num_tiles, attn.p, (int)attn.ld, heads_, kv_heads_, dk_, cache.page_size,
+                                                       cache.page_stride, cache.head_stride, cache.num_pages, window, scale_, ctx.status, sink_),
+                             "attention_prefill_sink");
+            }
+            if (ctx.small_tokens)      // the decoded tokens beside them: token by token, split over their keys
+                paged(ctx, q, cache, tables, attn, ctx.num_small, plans::attention_paged_splits(ctx.num_small, heads_, kv_heads_, longest, dk_), window, nullptr,
+                      ctx.small_tokens);
+        } else {
+            paged(ctx, q, cache, tables, attn, T, plans::attention_paged_splits(T, heads_, kv_heads_, longest, dk_), window, ctx.seq_context, nullptr);
+        }
         const Rows o = out_(ctx, attn, /*out_f32=*/true);
         Delta d;
         d.p = o.p;
@@ -112,11 +154,22 @@ public:
     }
 
 private:
-    size_t sink_scratch_bytes() const { return 0; }
-    void attend(const StepContext& ctx, const void* q, const CacheView& cache, const GroupTables& tables, const Rows& attn, int window) const {
-        launch_check(eg_sink_attention(ctx.stream, (int)ctx.dtype, q, cache.k, tables.block_table, tables.table_width, ctx.token_seq, ctx.positions, nullptr,
-                                       attn.p, attn.ld, ctx.num_tokens, heads_, kv_heads_, dk_, dv_, cache.page_size, cache.page_stride, cache.num_pages, window,
-                                       scale_, has_sink_ ? 1 : 0, sink_, ctx.status), "sink_attention");
+    void paged(const StepContext& ctx, const Rows& q, const CacheView& cache, const GroupTables& tables, const Rows& attn, int tokens, int splits, int window,
+               const int* seq_context, const int* token_list) const {
+        float *acc = nullptr, *ml = nullptr;
+        int* counters = nullptr;
+        if (splits > 1) {
+            const size_t T = (size_t)ctx.num_tokens;
+            acc = ctx.take<float>(T * heads_ * splits * dv_);
+            ml = ctx.take<float>(T * heads_ * splits * 2);
+            if ((size_t)tokens * kv_heads_ * ((heads_ / kv_heads_ + 15) / 16) > KernelScratch::ATTENTION_COUNTERS)
+                throw DeviceError("a step has more (token, KV head) pairs than the attention's ticket counters");
+            counters = ctx.scratch->attention_counters.as<int>();
+        }
+        launch_check(eg_attention_paged_sink(ctx.stream, q.p, (int)q.ld, cache.k, cache.v, tables.block_table, tables.table_width, ctx.token_seq, ctx.positions,
+                                             seq_context, attn.p, (int)attn.ld, acc, ml, tokens, heads_, kv_heads_, dk_, cache.page_size, cache.page_stride,
+                                             cache.head_stride, cache.num_pages, window, scale_, splits, ctx.status, counters, plans::use_pdl(), token_list, sink_),
+                     "attention_paged_sink");
     }
 
     int hidden_, heads_, kv_heads_, dk_, dv_;

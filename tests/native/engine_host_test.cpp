@@ -257,6 +257,72 @@ int main(int argc, char** argv) {
         CHECK(throws<std::invalid_argument>([&] { bad.validate(); }, "names stream addition 3"));
     }
 
+    // ---- a second listed design: branches normed on both sides, a shift in front of the mixer, a loop without additions -----------
+    {
+        const char* kListed = R"({"architecture": "Lasizen", "vocab": 83, "width": 48, "norm": {"eps": 2e-6}, "embedding": {"scale": 3.0},
+          "logit_scale": 0.5, "loop": {"start": 0, "stop": 2, "times": 3},
+          "layers": [
+            {"type": "attention", "mixer": {"heads": 6, "kv_heads": 2, "dim": 16, "vdim": 24, "scale": 0.2, "mask": {"size": 20},
+                                            "rot": {"base": 5000.0, "dims": 8, "scaling": {"factor": 4.0, "original": 64, "fast": 16.0, "slow": 2.0}}},
+             "mlp": {"kind": "dense", "ff": 72}},
+            {"type": "delta", "mixer": {"heads": 4, "kv_heads": 2, "dim": 12, "vdim": 20, "conv": 3}, "mlp": null},
+            {"type": "attention", "mixer": {"heads": 2, "kv_heads": 2, "dim": 8, "vdim": 8, "scale": 0.35}, "mlp": {"kind": "dense", "ff": 40}}]})";
+        const ModelSpec spec = ArchitectureRegistry::instance().build(json::parse(kListed));
+        CHECK(spec.architecture == "lasizen" && spec.layers.size() == 3 && spec.vocab_size == 83 && spec.hidden_size == 48);
+        // layers 0 and 1 three times in a row with a cache or state of their own each time, then layer 2; nothing is added between passes
+        CHECK(spec.run_order.size() == 7 && spec.stream_adds.empty());
+        const int layers[] = {0, 1, 0, 1, 0, 1, 2};
+        for (size_t i = 0; i < spec.run_order.size(); ++i)
+            CHECK(spec.run_order[i].layer == layers[i] && spec.run_order[i].cache == (int)i && spec.run_order[i].writes_cache && spec.run_order[i].stream_add < 0);
+        const SubLayerSpec& mix = spec.layers[0].sublayers[0];
+        CHECK(!spec.layers[0].parallel && spec.layers[0].sublayers.size() == 2 && spec.layers[1].sublayers.size() == 1);
+        CHECK(mix.part.kind == "sink_attention" && mix.part.prefix == "l0.mix" && mix.part.params.integer("heads") == 6 && mix.part.params.integer("kv_heads") == 2 &&
+              mix.part.params.integer("dim") == 16 && mix.part.params.integer("vdim") == 24 && mix.part.params.real("scale") == 0.2 &&
+              mix.part.params.integer("window") == 20 && mix.part.params.real("sink_logit") == 0.0 && mix.part.params.real("unit_eps") == 2e-6);
+        CHECK(mix.norm.kind == "rmsnorm" && mix.norm.prefix == "l0.norm1" && mix.norm.params.text("weight_name", "x") == "" && mix.norm_placement == "pre" &&
+              mix.output_norm.present && mix.output_norm.prefix == "l0.norm1b" && mix.output_norm.params.real("eps") == 2e-6);
+        CHECK(mix.shift.present && mix.shift.kind == "token_shift" && mix.shift.prefix == "l0.shift" && mix.shift.params.integer("size") == 48);
+        const PartSpec& rope = spec.layers[0].position;
+        CHECK(rope.present && rope.kind == "rope" && rope.params.integer("rotary_dim") == 8 && rope.params.integer("head_dim") == 16 && rope.params.real("theta") == 5000.0 &&
+              rope.params.real("scaling_factor") == 4.0 && rope.params.real("scaling_original") == 64.0 && rope.params.real("scaling_fast") == 16.0 &&
+              rope.params.real("scaling_slow") == 2.0);
+        const SubLayerSpec& ff = spec.layers[0].sublayers[1];
+        CHECK(ff.part.kind == "xielu" && ff.part.prefix == "l0.mlp" && ff.part.params.integer("ff") == 72 && ff.norm.prefix == "l0.norm2" &&
+              ff.output_norm.prefix == "l0.norm2b" && !ff.shift.present);
+        const PartSpec& delta = spec.layers[1].sublayers[0].part;
+        CHECK(delta.kind == "gated_delta" && delta.params.integer("heads") == 4 && delta.params.integer("kv_heads") == 2 && delta.params.integer("dim") == 12 &&
+              delta.params.integer("vdim") == 20 && delta.params.integer("conv") == 3 && delta.params.real("eps") == 2e-6 && delta.params.real("unit_eps") == 1e-6);
+        CHECK(spec.layers[1].sublayers[0].shift.present && !spec.layers[1].position.present);
+        // no window, no rotation: the keys say so by their absence
+        CHECK(!spec.layers[2].sublayers[0].part.params.has("window") && !spec.layers[2].position.present);
+        CHECK(spec.embedding.params.real("scale") == 3.0 && spec.lm_head.params.real("scale") == 0.5 && spec.embedding.prefix == "embed" &&
+              spec.final_norm.kind == "rmsnorm" && spec.final_norm.prefix == "final.norm" && spec.lm_head.prefix == "head");
+        auto listed = [&](const std::string& from, const std::string& to) {
+            std::string text = kListed;
+            const size_t at = text.find(from);
+            if (at == std::string::npos) throw std::logic_error("the test's configuration has no " + from);
+            text.replace(at, from.size(), to);
+            return ArchitectureRegistry::instance().build(json::parse(text));
+        };
+        const std::string loop = "\"loop\": {\"start\": 0, \"stop\": 2, \"times\": 3},";
+        CHECK(listed(loop, "").run_order.size() == 3);
+        CHECK(listed(loop, "\"loop\": {\"start\": 1, \"stop\": 3, \"times\": 2},").run_order.size() == 5);
+        CHECK(listed(loop, "\"loop\": {\"start\": 1, \"stop\": 1, \"times\": 4},").run_order.size() == 3);
+        CHECK(!listed("\"logit_scale\": 0.5,", "").lm_head.params.has("scale"));
+        CHECK(!listed(", \"scaling\": {\"factor\": 4.0, \"original\": 64, \"fast\": 16.0, \"slow\": 2.0}", "").layers[0].position.params.has("scaling_factor"));
+        CHECK(throws<ConfigError>([&] { listed(loop, "\"loop\": {\"start\": 2, \"stop\": 1, \"times\": 2},"); }, "loop must have"));
+        CHECK(throws<ConfigError>([&] { listed("\"heads\": 6", "\"heads\": 5"); }, "heads a multiple of kv_heads"));
+        CHECK(throws<ConfigError>([&] { listed("\"dims\": 8", "\"dims\": 7"); }, "rot.dims must be even"));
+        CHECK(throws<ConfigError>([&] { listed("\"conv\": 3", "\"conv\": 3.5"); }, "layers[1].mixer.conv must be an integer"));
+        CHECK(throws<ConfigError>([&] { listed("\"kind\": \"dense\", \"ff\": 72", "\"kind\": \"moe\", \"ff\": 72"); }, "kind must be 'dense'"));
+        CHECK(throws<ConfigError>([&] { listed("\"type\": \"delta\"", "\"type\": \"mamba1\""); }, "is no mixer of this design"));
+        CHECK(throws<ConfigError>([&] { listed("{\"size\": 20}", "{\"size\": 0}"); }, "mask.size must be > 0"));
+        // a shift belongs in front of a mixer, behind the norm in front of it
+        ModelSpec bad = spec;
+        bad.layers[0].sublayers[1].shift = bad.layers[0].sublayers[0].shift;
+        CHECK(throws<std::invalid_argument>([&] { bad.validate(); }, "a shift stands in front of a mixer"));
+    }
+
     if (failures) {
         std::printf("%d checks failed\n", failures);
         return 1;

@@ -161,7 +161,7 @@ def run_order(config):
 def forward(config, w, tokens, return_layers=False):
     """Logits [n, vocab] of a whole sequence (and the stream after every layer run)."""
     eps = config["norm"]["eps"]
-    x = w["embed"][np.asarray(tokens)] * config["embedding"]["scale"]
+    x = w["embed"][np.asarray(tokens)] * (config.get("embedding") or {}).get("scale", 1.0)
     streams = []
     for i in run_order(config):
         layer, p = config["layers"][i], f"l{i}."
