@@ -29,10 +29,15 @@ For profiling and for further sizes (one short line each, never the JSON line ab
 
     python bench.py --only decode|prefill|timeline|gemm|attention|serve [--batch B] [--layers L] [--context C] [--sizes 0.5b|1.5b|7b]
     python bench.py --only gufanex [--batch B] [--context C] [--steps K] [--sizes small|medium]
+    python bench.py --only lasizen [--batch B] [--context C] [--steps K] [--sizes small|medium]
 
 `gufanex` measures the Gufanex decoder (selective-scan and latent-attention layers with routed experts) at layer sizes
 of real models of those kinds, with random weights, beside a Qwen2 decoder of the same width, depth and active
 feed-forward size: one prompt of 2,048 tokens as one step, and decode steps of a batch at a context.
+
+`lasizen` measures the Lasizen decoder (windowed attention with a sink, gated delta-rule mixers, xIELU feed-forwards,
+norms on both sides of every branch) the same way, beside a Qwen2 decoder of the same width, depth, heads and
+feed-forward weights.
 
 `serve` runs 64 concurrent requests (prompts of 128..4096 tokens in portions of 512 beside
 decoding requests, 512 new tokens each) through the engine and reports wall-clock tokens a second.
@@ -86,6 +91,25 @@ def gufanex_bench_configs(size):
     qwen = dict(CONFIG_05B, num_hidden_layers=6, hidden_size=width, num_attention_heads=16 // k, num_key_value_heads=16 // k, head_dim=128,
                 intermediate_size=(top + 2) * ff, vocab_size=32000, tie_word_embeddings=False)
     return gufanex, qwen
+
+
+# Layer sizes for `--only lasizen`: attention of 16 heads of 128 over 4 key heads with a window of 1,024, delta-rule mixers of
+# 16 heads with 128 x 128 states, a dense feed-forward of four times the width ("medium"), and half of the width, heads and
+# feed-forward ("small").  Four layers, the middle two (an attention and a delta layer) passed twice: six layer runs.  The
+# Qwen2 decoder beside it has the same width, layer runs and heads, and a SwiGLU feed-forward with as many weights.
+def lasizen_bench_configs(size):
+    k = {"medium": 1, "small": 2}[size]
+    width, heads = 2048 // k, 16 // k
+    attention = {"type": "attention", "mixer": {"heads": heads, "kv_heads": 4 // k, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "mask": {"size": 1024},
+                                                "rot": {"base": 1000000.0, "dims": 64, "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}}
+    delta = {"type": "delta", "mixer": {"heads": heads, "kv_heads": heads // 2, "dim": 128, "vdim": 128, "conv": 4}}
+    mlp = {"kind": "dense", "ff": 4 * width}
+    lasizen = {"architecture": "Lasizen", "vocab": 32000, "width": width, "norm": {"eps": 1e-6}, "embedding": {"scale": float(width) ** 0.5},
+               "logit_scale": 1.0 / float(width) ** 0.5, "loop": {"start": 1, "stop": 3, "times": 2},
+               "layers": [dict(attention, mlp=mlp), dict(attention, mlp=mlp), dict(delta, mlp=mlp), dict(attention, mlp=mlp)]}
+    qwen = dict(CONFIG_05B, num_hidden_layers=6, hidden_size=width, num_attention_heads=heads, num_key_value_heads=4 // k, head_dim=128,
+                intermediate_size=(8 * width // 3 + 127) // 128 * 128, vocab_size=32000, tie_word_embeddings=False)
+    return lasizen, qwen
 
 
 CONTEXT = 4096
@@ -269,7 +293,10 @@ def measure_prefill(folder, config, repeats=5):
 def gufanex_folder(config, seed=0):
     import hashlib
 
-    from easy_gpt.cpp_b200.weights.gufanex_init import write_random_model
+    if config.get("architecture") == "Lasizen":
+        from easy_gpt.cpp_b200.weights.lasizen_init import write_random_model
+    else:
+        from easy_gpt.cpp_b200.weights.gufanex_init import write_random_model
 
     tag = hashlib.sha256(json.dumps(config, sort_keys=True).encode()).hexdigest()[:12]
     folder = Path(tempfile.gettempdir()) / f"easy_gpt_bench_{os.getuid()}_{tag}_{seed}"
@@ -582,9 +609,27 @@ def run_gufanex(args):
     return 0
 
 
+def run_lasizen(args):
+    size = args.sizes if args.sizes in ("small", "medium") else "medium"
+    lasizen, qwen = lasizen_bench_configs(size)
+    context = min(args.context, 2048) if args.context == CONTEXT else args.context
+    out = {"only": "lasizen", "sizes": size, "batch": args.batch, "context": context, "prefill_tokens": PREFILL_TOKENS, "dtype": "bfloat16",
+           "data": "synthetic (random weights)"}
+    with ClockSampler() as clocks:
+        if args.model in ("both", "lasizen"):
+            out["lasizen"] = measure_prefill_and_decode(gufanex_folder(lasizen), lasizen["vocab"], args.batch, context, args.steps, args.warmup)
+        if args.model in ("both", "qwen2"):
+            out["qwen2_equal"] = measure_prefill_and_decode(model_folder(qwen), qwen["vocab_size"], args.batch, context, args.steps, args.warmup)
+    out["clocks"] = clocks.summary()
+    print(json.dumps(out))
+    return 0
+
+
 def run_ours(args):
     if args.only == "gufanex":
         return run_gufanex(args)
+    if args.only == "lasizen":
+        return run_lasizen(args)
     config = dict(CONFIG_05B, **SIZES[args.sizes])
     if args.sizes != "0.5b" and not args.only:
         print("bench.py: --sizes other than 0.5b goes with --only (the JSON line is defined for the 0.5B sizes)")
@@ -712,15 +757,16 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration (named in config)")
     ap.add_argument("--context", type=int, default=CONTEXT, help="context length the decode steps end at (default 4096)")
-    ap.add_argument("--sizes", choices=list(SIZES) + ["small", "medium"], default="0.5b", help="layer sizes for --only runs (small, medium: --only gufanex)")
-    ap.add_argument("--model", choices=["both", "gufanex", "qwen2"], default="both", help="with --only gufanex: which of the two models to measure")
+    ap.add_argument("--sizes", choices=list(SIZES) + ["small", "medium"], default="0.5b", help="layer sizes for --only runs (small, medium: --only gufanex and --only lasizen)")
+    ap.add_argument("--model", choices=["both", "gufanex", "lasizen", "qwen2"], default="both",
+                    help="with --only gufanex or --only lasizen: which of the two models to measure")
     ap.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16", help="precision of --only decode")
     ap.add_argument("--default-options", action="store_true",
                     help="--only decode with the engine's default page size and request length")
     ap.add_argument("--ref-prompt", type=int, default=0,
                     help="prompt length of the reference arm (0: 1536, or the longest its int-indexed logits allow)")
     ap.add_argument("--fused", action="store_true", help="with --only timeline or decode: the decode step as one persistent kernel (EASY_GPT_FUSED_DECODE=1)")
-    ap.add_argument("--only", choices=["decode", "prefill", "timeline", "gemm", "attention", "serve", "gufanex"], default=None,
+    ap.add_argument("--only", choices=["decode", "prefill", "timeline", "gemm", "attention", "serve", "gufanex", "lasizen"], default=None,
                     help="measure one part only and print a short line (for profiling runs)")
     args = ap.parse_args()
     if args.gpus != 1:

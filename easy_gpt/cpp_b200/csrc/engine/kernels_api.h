@@ -147,8 +147,10 @@ int eg_attention_paged_sink(cudaStream_t stream, const void* q, int ldq, const v
 int eg_attention_prefill_sink(cudaStream_t stream, const void* q, int ldq, const void* k_cache, const void* v_cache, const int* block_table, int table_stride, const int* positions, const int* tiles, int num_tiles, void* out, int ldo, int num_heads, int num_kv_heads, int head_dim, int page_size, long long page_stride, long long head_stride, int num_pages, int window, float scale, int* status, float sink_logit);
 // attention_tcgen05.cu
 int eg_attention_prefill_tcgen05_sink(cudaStream_t stream, const void* q, long long ldq, int total_tokens, const void* k_cache, const void* v_cache, const int* block_table, int table_stride, const int* positions, const int* tiles, int num_tiles, void* out, long long ldo, int num_heads, int num_kv_heads, int head_dim, int page_size, long long page_stride, long long head_stride, int num_pages, int window, float scale, int* status, int max_parts, int part_tiles, float* partial_o, float* partial_ml, int* queue, float sink_logit);
+// gemm_tcgen05.cu
+int eg_gemm_tcgen05_pair_xielu(cudaStream_t stream, const void* A, long long lda, const void* W, long long ldw, void* out, long long ldo, int M, int N, int K, int tile_n, int* status, float act_a, float act_b);
 // gated_delta.cu
 int eg_gated_delta_plan(int dk, int dv, int* rows_per_lane, int* lanes);
 // gated_delta.cu
-int eg_gated_delta(cudaStream_t stream, const float* qkv, long long ldq, int q_col, int k_col, int v_col, const float* proj, long long ldp, int b_col, int a_col, int z_col, const float* a_log, const float* dt_bias, const float* norm_w, float* state, long long slot_floats, long long state_offset, const int* seq_starts, const int* seq_slots, void* y, int y_dtype, long long ldy, int num_seqs, int heads, int kv_heads, int dk, int dv, float unit_eps, float eps);
+int eg_gated_delta(cudaStream_t stream, const float* qkv, long long ldq, int q_col, int k_col, int v_col, const float* proj, long long ldp, int b_col, int a_col, int z_col, const float* a_log, const float* dt_bias, const float* norm_w, float* state, long long slot_floats, long long state_offset, const int* seq_starts, const int* seq_slots, void* y, int y_dtype, long long ldy, float* o_raw, int slices, int tokens, int num_seqs, int heads, int kv_heads, int dk, int dv, float unit_eps, float eps);
 }  // extern "C"

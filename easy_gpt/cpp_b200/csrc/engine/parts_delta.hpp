@@ -233,7 +233,7 @@ public:
     }
     size_t weight_bytes() const override { return in_.weight_bytes() + out_.weight_bytes() + (size_t)channels() * taps_ * 4; }
     size_t arena_bytes(long long T) const override {
-        return (size_t)T * ((size_t)in_.out_features * 4 + (size_t)channels() * 4 + (size_t)heads_ * dv_ * 4 + (size_t)hidden_ * 4) + (1u << 16);
+        return (size_t)T * ((size_t)in_.out_features * 4 + (size_t)channels() * 4 + (size_t)heads_ * dv_ * 8 + (size_t)hidden_ * 4) + (1u << 16);
     }
     bool capturable() const override { return true; }
     long long conv_floats() const { return (long long)(taps_ - 1) * channels(); }
@@ -256,9 +256,13 @@ public:
         launch_check(eg_conv_state(ctx.stream, (int)DType::F32, proj.p, proj.ld, state, slot, ctx.seq_starts, ctx.seq_slots, ctx.num_seqs, C, taps_), "conv_state");
         Rows y{ctx.take_rows(T, heads_ * dv_, dtype), dtype, T, heads_ * dv_, heads_ * dv_};
         const int qk = kv_heads_ * dk_, z_col = C, b_col = C + heads_ * dv_, a_col = b_col + heads_;
+        // few (entry, head) pairs: a head's columns are dealt to several blocks (they do not depend on one another), and the
+        // norm over a head's outputs becomes a kernel of its own.  The count depends on the step's size alone.
+        const int slices = plans::delta_column_slices(ctx.num_seqs, heads_, dv_);
+        float* o_raw = slices > 1 ? ctx.take<float>((size_t)T * heads_ * dv_) : nullptr;
         launch_check(eg_gated_delta(ctx.stream, u, C, 0, qk, 2 * qk, (const float*)proj.p, proj.ld, b_col, a_col, z_col, a_log_.as<float>(), dt_bias_.as<float>(),
-                                    norm_w_.as<float>(), state, slot, conv_floats(), ctx.seq_starts, ctx.seq_slots, y.p, (int)dtype, y.ld, ctx.num_seqs, heads_,
-                                    kv_heads_, dk_, dv_, unit_eps_, eps_), "gated_delta");
+                                    norm_w_.as<float>(), state, slot, conv_floats(), ctx.seq_starts, ctx.seq_slots, y.p, (int)dtype, y.ld, o_raw, slices, T,
+                                    ctx.num_seqs, heads_, kv_heads_, dk_, dv_, unit_eps_, eps_), "gated_delta");
         const Rows o = out_(ctx, y, /*out_f32=*/true);
         Delta d;
         d.p = o.p;
@@ -300,9 +304,15 @@ public:
         const int T = ctx.num_tokens;
         const DType dtype = ctx.dtype;
         const Rows h = in.pending ? in.pending->materialize() : in.rows;
-        const Rows z = up_(ctx, h, /*out_f32=*/true);
         Rows act{ctx.take_rows(T, ff_, dtype), dtype, T, ff_, ff_};
-        launch_check(eg_xielu(ctx.stream, z.p, (int)z.dtype, z.ld, act.p, (int)dtype, act.ld, T, ff_, above_, below_), "xielu");
+        if (plans::gemm_tcgen05_wide_takes(dtype, T, ff_, hidden_) && Linear::aligned(h)) {
+            // prompts: the product on the tcgen05 tensor cores (CTA pairs, 256 x 256 tiles) with the activation in its epilogue
+            launch_check(eg_gemm_tcgen05_pair_xielu(ctx.stream, h.p, h.ld, up_.weight, hidden_, act.p, ff_, T, ff_, hidden_, 256, ctx.status, above_, below_),
+                         "gemm_tcgen05_pair_xielu");
+        } else {
+            const Rows z = up_(ctx, h, /*out_f32=*/true);
+            launch_check(eg_xielu(ctx.stream, z.p, (int)z.dtype, z.ld, act.p, (int)dtype, act.ld, T, ff_, above_, below_), "xielu");
+        }
         const Rows o = down_(ctx, act, /*out_f32=*/true);
         Delta d;
         d.p = o.p;

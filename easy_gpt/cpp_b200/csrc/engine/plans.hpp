@@ -30,7 +30,7 @@ inline int use_pdl() {
     }
     return mode;
 }
-enum Epilogue { EPI_STORE = 0, EPI_F32 = 1, EPI_SWIGLU = 2, EPI_QKV_ROPE = 3, EPI_RESID_NORM = 4 };
+enum Epilogue { EPI_STORE = 0, EPI_F32 = 1, EPI_SWIGLU = 2, EPI_QKV_ROPE = 3, EPI_RESID_NORM = 4, EPI_XIELU = 5 };
 
 inline int sm_count() {
     static int count = 0;
@@ -177,6 +177,14 @@ inline bool moe_grouped_takes(DType dtype, int tokens, int width, int ff, int ex
 // 4,096 channels x 16 states, a prompt of 2,048 tokens, ms for all layers' scans with 1 / 2 / 4 / 8 / 16 states a thread:
 // 1.8 / 2.3 / 4.0 / 7.2 / 13.6).  It hangs off the mixer's sizes alone, never off the
 // batch, so the order of the sum over a channel's states is the same in every step.
+// Into how many blocks the delta rule's kernel cuts a head's columns: until the step has about two blocks an SM, at least
+// eight columns a block.
+inline int delta_column_slices(int entries, int heads, int value_dim) {
+    const long long blocks = (long long)std::max(1, entries) * heads;
+    const long long wanted = (2LL * sm_count() + blocks - 1) / blocks;
+    return (int)std::max<long long>(1, std::min<long long>(wanted, value_dim / 8));
+}
+
 inline int scan_states_per_lane(int channels, int states) {
     static int forced = -1;                     // EASY_GPT_SCAN_STATES_PER_LANE, for measurements
     if (forced < 0) {

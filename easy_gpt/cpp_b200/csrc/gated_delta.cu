@@ -42,29 +42,35 @@ __device__ __forceinline__ float decay_exp(float x) {
 }
 
 constexpr int TILE = 16;        // tokens staged at a time
+constexpr int PAD = 4;          // floats between the parts' rows of a staged key or query: the parts' 16-byte loads then hit different banks
 
+// grid (heads, entries, column slices): a block holds `cols` columns of a head's S.  With o_raw the block leaves its columns
+// of o there (float32) and the norm over the head's columns is another kernel's; without, the block holds whole heads and
+// norms and gates its outputs itself.
 template <typename TO, int R, int P>
 __global__ void __launch_bounds__(1024) gated_delta_kernel(const float* __restrict__ qkv, long long ldq, int q_col, int k_col, int v_col,
                                                            const float* __restrict__ proj, long long ldp, int b_col, int a_col, int z_col,
                                                            const float* __restrict__ a_log, const float* __restrict__ dt_bias,
                                                            const float* __restrict__ norm_w, float* __restrict__ state, long long slot_floats,
                                                            long long state_offset, const int* __restrict__ seq_starts,
-                                                           const int* __restrict__ seq_slots, TO* __restrict__ y, long long ldy, int heads,
-                                                           int kv_heads, int dk, int dv, float unit_eps, float eps) {
+                                                           const int* __restrict__ seq_slots, TO* __restrict__ y, long long ldy,
+                                                           float* __restrict__ o_raw, int cols, int heads, int kv_heads, int dk, int dv,
+                                                           float unit_eps, float eps) {
     extern __shared__ float smem[];
-    const int dkp = R * P;                          // dk padded: rows beyond dk see zero keys and queries and stay zero
-    float* s_k = smem;                              // [TILE, dkp]
-    float* s_q = s_k + TILE * dkp;                  // [TILE, dkp]
-    float* s_v = s_q + TILE * dkp;                  // [TILE, dv]
-    float* s_o = s_v + TILE * dv;                   // [TILE, dv]
-    float* s_beta = s_o + TILE * dv;                // [TILE]
+    constexpr int RS = R + PAD, DKS = RS * P;       // a part's stride, a staged row's length (rows beyond dk hold zeros)
+    float* s_k = smem;                              // [TILE, DKS]
+    float* s_q = s_k + TILE * DKS;                  // [TILE, DKS]
+    float* s_v = s_q + TILE * DKS;                  // [TILE, cols]
+    float* s_o = s_v + TILE * cols;                 // [TILE, cols]
+    float* s_beta = s_o + TILE * cols;              // [TILE]
     float* s_g = s_beta + TILE;
     float* s_kq = s_g + TILE;
-    const int head = blockIdx.x, seq = blockIdx.y;
+    const int head = blockIdx.x, seq = blockIdx.y, j0 = blockIdx.z * cols;
     const int kvh = head / (heads / kv_heads);
     const int start = seq_starts[seq], count = seq_starts[seq + 1] - start;
-    const int j = threadIdx.x / P, part = threadIdx.x % P;
-    const bool active = j < dv;
+    const int jl = threadIdx.x / P, j = j0 + jl, part = threadIdx.x % P;
+    const int width = min(cols, dv - j0);           // this block's columns
+    const bool active = jl < width;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
     float* S = state + (size_t)seq_slots[seq] * slot_floats + state_offset + ((size_t)head * dv + (active ? j : 0)) * dk;
     float s[R];
@@ -77,15 +83,16 @@ __global__ void __launch_bounds__(1024) gated_delta_kernel(const float* __restri
     for (int t0 = 0; t0 < count; t0 += TILE) {
         const int n = min(TILE, count - t0);
         __syncthreads();                            // the tile before is done with shared memory
-        for (int i = threadIdx.x; i < n * dkp; i += blockDim.x) {
-            const int t = i / dkp, d = i % dkp;
+        for (int i = threadIdx.x; i < n * R * P; i += blockDim.x) {
+            const int t = i / (R * P), d = i % (R * P);
             const float* row = qkv + (size_t)(start + t0 + t) * ldq;
-            s_k[i] = d < dk ? row[k_col + kvh * dk + d] : 0.f;
-            s_q[i] = d < dk ? row[q_col + kvh * dk + d] : 0.f;
+            const int at = t * DKS + (d / R) * RS + d % R;
+            s_k[at] = d < dk ? row[k_col + kvh * dk + d] : 0.f;
+            s_q[at] = d < dk ? row[q_col + kvh * dk + d] : 0.f;
         }
-        for (int i = threadIdx.x; i < n * dv; i += blockDim.x) {
-            const int t = i / dv, d = i % dv;
-            s_v[i] = qkv[(size_t)(start + t0 + t) * ldq + v_col + head * dv + d];
+        for (int i = threadIdx.x; i < n * width; i += blockDim.x) {
+            const int t = i / width, d = i % width;
+            s_v[t * cols + d] = qkv[(size_t)(start + t0 + t) * ldq + v_col + head * dv + j0 + d];
         }
         if (threadIdx.x < n) {
             const float* row = proj + (size_t)(start + t0 + threadIdx.x) * ldp;
@@ -96,8 +103,9 @@ __global__ void __launch_bounds__(1024) gated_delta_kernel(const float* __restri
         // unit keys and queries, and k^ . q^, a warp per token
         for (int t = warp; t < n; t += warps) {
             float kk = 0.f, qq = 0.f, kq = 0.f;
-            for (int d = lane; d < dkp; d += 32) {
-                const float a = s_k[t * dkp + d], b = s_q[t * dkp + d];
+            for (int d = lane; d < R * P; d += 32) {
+                const int at = t * DKS + (d / R) * RS + d % R;
+                const float a = s_k[at], b = s_q[at];
                 kk = fmaf(a, a, kk);
                 qq = fmaf(b, b, qq);
                 kq = fmaf(a, b, kq);
@@ -106,43 +114,55 @@ __global__ void __launch_bounds__(1024) gated_delta_kernel(const float* __restri
             qq = warp_sum(qq);
             kq = warp_sum(kq);
             const float ik = 1.0f / sqrtf(kk + unit_eps), iq = q_scale / sqrtf(qq + unit_eps);
-            for (int d = lane; d < dkp; d += 32) {
-                s_k[t * dkp + d] *= ik;
-                s_q[t * dkp + d] *= iq;
+            for (int d = lane; d < R * P; d += 32) {
+                const int at = t * DKS + (d / R) * RS + d % R;
+                s_k[at] *= ik;
+                s_q[at] *= iq;
             }
             if (lane == 0) s_kq[t] = kq * ik * iq;
         }
         __syncthreads();
         for (int t = 0; t < n; ++t) {
-            const float* kt = s_k + t * dkp + part * R;
-            const float* qt = s_q + t * dkp + part * R;
-            float sk = 0.f, sq = 0.f;
+            const float4* kt = reinterpret_cast<const float4*>(s_k + t * DKS + part * RS);
+            const float4* qt = reinterpret_cast<const float4*>(s_q + t * DKS + part * RS);
+            float kv[R];
+            float sk0 = 0.f, sk1 = 0.f, sq0 = 0.f, sq1 = 0.f;
 #pragma unroll
-            for (int r = 0; r < R; ++r) {
-                sk = fmaf(s[r], kt[r], sk);
-                sq = fmaf(s[r], qt[r], sq);
+            for (int r = 0; r < R; r += 4) {
+                const float4 a = kt[r / 4], b = qt[r / 4];
+                kv[r] = a.x; kv[r + 1] = a.y; kv[r + 2] = a.z; kv[r + 3] = a.w;
+                sk0 = fmaf(s[r], a.x, sk0); sk1 = fmaf(s[r + 1], a.y, sk1); sk0 = fmaf(s[r + 2], a.z, sk0); sk1 = fmaf(s[r + 3], a.w, sk1);
+                sq0 = fmaf(s[r], b.x, sq0); sq1 = fmaf(s[r + 1], b.y, sq1); sq0 = fmaf(s[r + 2], b.z, sq0); sq1 = fmaf(s[r + 3], b.w, sq1);
             }
+            float sk = sk0 + sk1, sq = sq0 + sq1;
 #pragma unroll
             for (int o = 1; o < P; o <<= 1) {
                 sk += __shfl_xor_sync(0xffffffffu, sk, o);
                 sq += __shfl_xor_sync(0xffffffffu, sq, o);
             }
             const float g = s_g[t];
-            const float u = s_beta[t] * ((active ? s_v[t * dv + j] : 0.f) - g * sk);
+            const float u = s_beta[t] * ((active ? s_v[t * cols + jl] : 0.f) - g * sk);
 #pragma unroll
-            for (int r = 0; r < R; ++r) s[r] = fmaf(kt[r], u, g * s[r]);
-            if (active && part == 0) s_o[t * dv + j] = fmaf(g, sq, u * s_kq[t]);
+            for (int r = 0; r < R; ++r) s[r] = fmaf(kv[r], u, g * s[r]);
+            if (active && part == 0) s_o[t * cols + jl] = fmaf(g, sq, u * s_kq[t]);
         }
         __syncthreads();
+        if (o_raw) {
+            for (int i = threadIdx.x; i < n * width; i += blockDim.x) {
+                const int t = i / width, d = i % width;
+                o_raw[(size_t)(start + t0 + t) * ((size_t)heads * dv) + head * dv + j0 + d] = s_o[t * cols + d];
+            }
+            continue;
+        }
         // y = o / rms(o) * w * silu(z), a warp per token
         for (int t = warp; t < n; t += warps) {
             float ss = 0.f;
-            for (int d = lane; d < dv; d += 32) ss = fmaf(s_o[t * dv + d], s_o[t * dv + d], ss);
+            for (int d = lane; d < dv; d += 32) ss = fmaf(s_o[t * cols + d], s_o[t * cols + d], ss);
             ss = warp_sum(ss);
             const float inv = 1.0f / sqrtf(ss / (float)dv + eps);
             const float* z = proj + (size_t)(start + t0 + t) * ldp + z_col + head * dv;
             TO* out = y + (size_t)(start + t0 + t) * ldy + head * dv;
-            for (int d = lane; d < dv; d += 32) out[d] = from_f32<TO>(s_o[t * dv + d] * inv * norm_w[d] * silu_f(z[d]));
+            for (int d = lane; d < dv; d += 32) out[d] = from_f32<TO>(s_o[t * cols + d] * inv * norm_w[d] * silu_f(z[d]));
         }
     }
     if (active) {
@@ -154,34 +174,62 @@ __global__ void __launch_bounds__(1024) gated_delta_kernel(const float* __restri
     }
 }
 
+// y = o / rms(o) * w * silu(z) per (token, head), a warp each: behind a recurrence whose blocks held slices of a head
+template <typename TO>
+__global__ void delta_output_kernel(const float* __restrict__ o_raw, const float* __restrict__ proj, long long ldp, int z_col,
+                                    const float* __restrict__ norm_w, TO* __restrict__ y, long long ldy, int tokens, int heads, int dv, float eps) {
+    const int lane = threadIdx.x & 31;
+    const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (w >= (long long)tokens * heads) return;
+    const int t = (int)(w / heads), head = (int)(w % heads);
+    const float* o = o_raw + ((size_t)t * heads + head) * dv;
+    float ss = 0.f;
+    for (int d = lane; d < dv; d += 32) ss = fmaf(o[d], o[d], ss);
+    ss = warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss / (float)dv + eps);
+    const float* z = proj + (size_t)t * ldp + z_col + head * dv;
+    TO* out = y + (size_t)t * ldy + head * dv;
+    for (int d = lane; d < dv; d += 32) out[d] = from_f32<TO>(o[d] * inv * norm_w[d] * silu_f(z[d]));
+}
+
 template <typename TO, int R, int P>
 int launch_delta(cudaStream_t stream, const float* qkv, long long ldq, int q_col, int k_col, int v_col, const float* proj, long long ldp, int b_col,
                  int a_col, int z_col, const float* a_log, const float* dt_bias, const float* norm_w, float* state, long long slot_floats,
-                 long long state_offset, const int* seq_starts, const int* seq_slots, void* y, long long ldy, int num_seqs, int heads, int kv_heads, int dk,
-                 int dv, float unit_eps, float eps) {
-    const int threads = (dv * P + 31) / 32 * 32;
-    const size_t smem = ((size_t)TILE * (2 * R * P + 2 * dv) + 3 * TILE) * sizeof(float);
+                 long long state_offset, const int* seq_starts, const int* seq_slots, void* y, long long ldy, float* o_raw, int slices, int tokens,
+                 int num_seqs, int heads, int kv_heads, int dk, int dv, float unit_eps, float eps) {
+    // columns per block: whole warps of them (32 / P columns a warp)
+    const int per_warp = 32 / P;
+    int cols = (dv + slices - 1) / slices;
+    cols = (cols + per_warp - 1) / per_warp * per_warp;
+    if (!o_raw) cols = (dv + per_warp - 1) / per_warp * per_warp;
+    slices = o_raw ? (dv + cols - 1) / cols : 1;
+    const int threads = cols * P;
+    const size_t smem = ((size_t)TILE * (2 * (R + PAD) * P + 2 * cols) + 3 * TILE) * sizeof(float);
     if (threads > 1024 || smem > 200 * 1024) return (int)cudaErrorInvalidValue;
     auto kernel = gated_delta_kernel<TO, R, P>;
     if (smem > 48 * 1024) {
         const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
     }
-    kernel<<<dim3(heads, num_seqs), threads, smem, stream>>>(qkv, ldq, q_col, k_col, v_col, proj, ldp, b_col, a_col, z_col, a_log, dt_bias, norm_w, state,
-                                                             slot_floats, state_offset, seq_starts, seq_slots, (TO*)y, ldy, heads, kv_heads, dk, dv, unit_eps,
-                                                             eps);
+    kernel<<<dim3(heads, num_seqs, slices), threads, smem, stream>>>(qkv, ldq, q_col, k_col, v_col, proj, ldp, b_col, a_col, z_col, a_log, dt_bias, norm_w,
+                                                                     state, slot_floats, state_offset, seq_starts, seq_slots, (TO*)y, ldy, o_raw, cols, heads,
+                                                                     kv_heads, dk, dv, unit_eps, eps);
+    if (o_raw) {
+        const long long warps = (long long)tokens * heads;
+        delta_output_kernel<TO><<<(unsigned)((warps + 3) / 4), 128, 0, stream>>>(o_raw, proj, ldp, z_col, norm_w, (TO*)y, ldy, tokens, heads, dv, eps);
+    }
     return eg_launch_status();
 }
 
 template <typename TO>
 int dispatch_delta(int R, int P, cudaStream_t stream, const float* qkv, long long ldq, int q_col, int k_col, int v_col, const float* proj, long long ldp,
                    int b_col, int a_col, int z_col, const float* a_log, const float* dt_bias, const float* norm_w, float* state, long long slot_floats,
-                   long long state_offset, const int* seq_starts, const int* seq_slots, void* y, long long ldy, int num_seqs, int heads, int kv_heads, int dk,
-                   int dv, float unit_eps, float eps) {
+                   long long state_offset, const int* seq_starts, const int* seq_slots, void* y, long long ldy, float* o_raw, int slices, int tokens,
+                   int num_seqs, int heads, int kv_heads, int dk, int dv, float unit_eps, float eps) {
 #define EG_DELTA(RR, PP)                                                                                                                                  \
     if (R == RR && P == PP)                                                                                                                               \
         return launch_delta<TO, RR, PP>(stream, qkv, ldq, q_col, k_col, v_col, proj, ldp, b_col, a_col, z_col, a_log, dt_bias, norm_w, state, slot_floats, \
-                                        state_offset, seq_starts, seq_slots, y, ldy, num_seqs, heads, kv_heads, dk, dv, unit_eps, eps)
+                                        state_offset, seq_starts, seq_slots, y, ldy, o_raw, slices, tokens, num_seqs, heads, kv_heads, dk, dv, unit_eps, eps)
     EG_DELTA(4, 4);
     EG_DELTA(8, 4);
     EG_DELTA(16, 4);
@@ -208,17 +256,19 @@ EG_API int eg_gated_delta_plan(int dk, int dv, int* rows_per_lane, int* lanes) {
 // qkv float32 [tokens, ldq]: convolved, activated queries (key heads x dk at q_col), keys (k_col) and values (heads x dv at
 // v_col).  proj float32 [tokens, ldp]: the projection's output with b (heads) at b_col, a (heads) at a_col and the output
 // gate z (heads x dv) at z_col.  state: the requests' slots; S of a request lies state_offset floats into its slot, as
-// [heads, dv, dk].  y [tokens, ldy] in y_dtype.
+// [heads, dv, dk].  y [tokens, ldy] in y_dtype.  slices > 1 (with o_raw, float32 [tokens, heads * dv]): a head's columns
+// are dealt to that many blocks, for steps with few (entry, head) pairs, and the outputs are normed by a second kernel.
 EG_API int eg_gated_delta(cudaStream_t stream, const float* qkv, long long ldq, int q_col, int k_col, int v_col, const float* proj, long long ldp,
                           int b_col, int a_col, int z_col, const float* a_log, const float* dt_bias, const float* norm_w, float* state,
                           long long slot_floats, long long state_offset, const int* seq_starts, const int* seq_slots, void* y, int y_dtype, long long ldy,
-                          int num_seqs, int heads, int kv_heads, int dk, int dv, float unit_eps, float eps) {
+                          float* o_raw, int slices, int tokens, int num_seqs, int heads, int kv_heads, int dk, int dv, float unit_eps, float eps) {
     if (num_seqs <= 0) return 0;
     int R = 0, P = 0;
-    if (kv_heads <= 0 || heads % kv_heads || !eg_gated_delta_plan(dk, dv, &R, &P)) return (int)cudaErrorInvalidValue;
+    if (kv_heads <= 0 || heads % kv_heads || !eg_gated_delta_plan(dk, dv, &R, &P) || slices < 1) return (int)cudaErrorInvalidValue;
+    if (slices == 1 || !o_raw) { o_raw = nullptr; slices = 1; }
     if (y_dtype == EG_BF16)
         return dispatch_delta<bf16>(R, P, stream, qkv, ldq, q_col, k_col, v_col, proj, ldp, b_col, a_col, z_col, a_log, dt_bias, norm_w, state, slot_floats,
-                                    state_offset, seq_starts, seq_slots, y, ldy, num_seqs, heads, kv_heads, dk, dv, unit_eps, eps);
+                                    state_offset, seq_starts, seq_slots, y, ldy, o_raw, slices, tokens, num_seqs, heads, kv_heads, dk, dv, unit_eps, eps);
     return dispatch_delta<float>(R, P, stream, qkv, ldq, q_col, k_col, v_col, proj, ldp, b_col, a_col, z_col, a_log, dt_bias, norm_w, state, slot_floats,
-                                 state_offset, seq_starts, seq_slots, y, ldy, num_seqs, heads, kv_heads, dk, dv, unit_eps, eps);
+                                 state_offset, seq_starts, seq_slots, y, ldy, o_raw, slices, tokens, num_seqs, heads, kv_heads, dk, dv, unit_eps, eps);
 }

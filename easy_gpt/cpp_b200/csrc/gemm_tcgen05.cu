@@ -43,7 +43,7 @@ constexpr int THREADS = 192;                                     // 6 warps
 constexpr int TMEM_COLS = 128;
 constexpr unsigned WAIT_LIMIT = 1u << 24;
 
-enum { EPI_STORE = 0, EPI_SWIGLU = 2 };
+enum { EPI_STORE = 0, EPI_SWIGLU = 2, EPI_XIELU = 5 };
 
 
 // Bounded wait: false if it gave up (or another role already did).
@@ -92,6 +92,14 @@ __device__ __forceinline__ float swiglu_fast(float g, float u) {
     return u * (g * r);
 }
 
+// xIELU for an epilogue whose result is rounded to bfloat16: the hardware's base-2 exponent for the branch below zero.
+__device__ __forceinline__ float xielu_fast(float z, float a, float b) {
+    if (z > 0.f) return fmaf(a * z, z, 0.5f * z);
+    float e;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(1.4426950408889634f * z));
+    return fmaf(b, (e - 1.0f) - z, 0.5f * z);
+}
+
 // Instruction descriptor for kind::f16: D float32, A and B bfloat16, both K-major, M = 128, N = BN.
 __device__ __forceinline__ uint32_t umma_idesc(int n = BN) {
     uint32_t d = 0;
@@ -114,6 +122,8 @@ struct Params {
     // grouped products (single-CTA kernel only): row tile i of A is multiplied by the W of group tile_group[i] (W holds
     // the groups' [N, K] matrices one after the other); a tile whose entry is negative has no rows and is skipped
     const int* tile_group;
+    // EPI_XIELU (pair kernel): out = a z^2 + z / 2 for z > 0, b (e^z - 1 - z) + z / 2 for z <= 0, element by element
+    float act_a = 0.f, act_b = 0.f;
 };
 
 __global__ void __launch_bounds__(THREADS)
@@ -643,6 +653,10 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                                          "r"(packed[4 * q + 2]), "r"(packed[4 * q + 3]) : "memory");
                         }
                     } else {
+                        if (p.epilogue == EPI_XIELU) {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) v[j] = xielu_fast(v[j], p.act_a, p.act_b);
+                        }
                         uint32_t packed[16];
 #pragma unroll
                         for (int j = 0; j < 16; ++j) {
@@ -1058,12 +1072,12 @@ int launch_pair(cudaStream_t stream, const CUtensorMap& map_a, const CUtensorMap
 
 // The same product on CTA pairs (tcgen05.mma.cta_group::2): tiles of 256 x tile_n, tile_n 256 or 128 (N % tile_n == 0),
 // K % 64 == 0; epilogues as eg_gemm_tcgen05 (SwiGLU with tile_n 256 only).
-EG_API int eg_gemm_tcgen05_pair(cudaStream_t stream, int epilogue, const void* A, long long lda, const void* W, long long ldw,
-                                const float* bias, void* out, long long ldo, int M, int N, int K, int tile_n, int* status,
-                                long long* trace) {
+static int gemm_tcgen05_pair_any(cudaStream_t stream, int epilogue, const void* A, long long lda, const void* W, long long ldw,
+                                 const float* bias, void* out, long long ldo, int M, int N, int K, int tile_n, int* status,
+                                 long long* trace, float act_a, float act_b) {
     if (M <= 0 || N <= 0) return 0;
     if ((tile_n != 128 && tile_n != 256) || N % tile_n || K % BK || K <= 0 || lda % 8 || ldw % 8 || ldo % 8 || (uintptr_t)A % 16 ||
-        (uintptr_t)W % 16 || (uintptr_t)out % 16 || (epilogue != EPI_STORE && epilogue != EPI_SWIGLU) ||
+        (uintptr_t)W % 16 || (uintptr_t)out % 16 || (epilogue != EPI_STORE && epilogue != EPI_SWIGLU && epilogue != EPI_XIELU) ||
         (epilogue == EPI_SWIGLU && tile_n != 256) || !status)
         return (int)cudaErrorInvalidValue;
     static int sm_count = 0;
@@ -1077,5 +1091,21 @@ EG_API int eg_gemm_tcgen05_pair(cudaStream_t stream, int epilogue, const void* A
         make_map(&map_out, out, M, epilogue == EPI_SWIGLU ? N / 2 : N, ldo, 32))
         return (int)cudaErrorInvalidValue;
     Params p{(bf16*)out, ldo, bias, M, N, K, epilogue, status, trace};
+    p.act_a = act_a;
+    p.act_b = act_b;
     return tile_n == 256 ? launch_pair<256>(stream, map_a, map_w, map_out, p, sm_count) : launch_pair<128>(stream, map_a, map_w, map_out, p, sm_count);
+}
+
+EG_API int eg_gemm_tcgen05_pair(cudaStream_t stream, int epilogue, const void* A, long long lda, const void* W, long long ldw,
+                                const float* bias, void* out, long long ldo, int M, int N, int K, int tile_n, int* status,
+                                long long* trace) {
+    if (epilogue == EPI_XIELU) return (int)cudaErrorInvalidValue;
+    return gemm_tcgen05_pair_any(stream, epilogue, A, lda, W, ldw, bias, out, ldo, M, N, K, tile_n, status, trace, 0.f, 0.f);
+}
+
+// The same product with the xIELU activation in its epilogue: out = act(A W^T), act(z) = a z^2 + z / 2 for z > 0 and
+// b (e^z - 1 - z) + z / 2 for z <= 0, bfloat16 [M, N].
+EG_API int eg_gemm_tcgen05_pair_xielu(cudaStream_t stream, const void* A, long long lda, const void* W, long long ldw, void* out, long long ldo, int M,
+                                      int N, int K, int tile_n, int* status, float act_a, float act_b) {
+    return gemm_tcgen05_pair_any(stream, EPI_XIELU, A, lda, W, ldw, nullptr, out, ldo, M, N, K, tile_n, status, nullptr, act_a, act_b);
 }
