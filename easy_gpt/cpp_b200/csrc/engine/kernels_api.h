@@ -132,6 +132,8 @@ int eg_rmsnorm_shift(cudaStream_t stream, const float* residual, const float* ga
 // sandwich.cu
 int eg_rmsnorm_add(cudaStream_t stream, float* residual, const void* y, int y_dtype, long long ldy, const float* gain, float eps, int tokens, int hidden);
 // sandwich.cu
+int eg_rmsnorm_add_norm(cudaStream_t stream, float* residual, const void* y, int y_dtype, long long ldy, const float* gain, float eps, const float* gain2, float eps2, void* out, int out_dtype, int tokens, int hidden);
+// sandwich.cu
 int eg_xielu(cudaStream_t stream, const void* x, int x_dtype, long long ldx, void* out, int out_dtype, long long ldo, int tokens, int n, float ap, float an);
 // sandwich.cu
 int eg_embedding_gather_scaled(cudaStream_t stream, int dtype, const int* ids, const void* table, float* residual, int tokens, int hidden, int vocab, float scale, int* status);
@@ -152,5 +154,5 @@ int eg_gemm_tcgen05_pair_xielu(cudaStream_t stream, const void* A, long long lda
 // gated_delta.cu
 int eg_gated_delta_plan(int dk, int dv, int* rows_per_lane, int* lanes);
 // gated_delta.cu
-int eg_gated_delta(cudaStream_t stream, const float* qkv, long long ldq, int q_col, int k_col, int v_col, const float* proj, long long ldp, int b_col, int a_col, int z_col, const float* a_log, const float* dt_bias, const float* norm_w, float* state, long long slot_floats, long long state_offset, const int* seq_starts, const int* seq_slots, void* y, int y_dtype, long long ldy, float* o_raw, int slices, int tokens, int num_seqs, int heads, int kv_heads, int dk, int dv, float unit_eps, float eps);
+int eg_gated_delta(cudaStream_t stream, float* qkv, long long ldq, int q_col, int k_col, int v_col, const float* proj, long long ldp, int b_col, int a_col, int z_col, const float* a_log, const float* dt_bias, const float* norm_w, float* state, long long slot_floats, long long state_offset, const int* seq_starts, const int* seq_slots, void* y, int y_dtype, long long ldy, float* aux, float* o_raw, int slices, int tokens, int num_seqs, int heads, int kv_heads, int dk, int dv, float unit_eps, float eps);
 }  // extern "C"

@@ -149,6 +149,7 @@ public:
         const int T = ctx.num_tokens;
         if (parallel) return forward_parallel(ctx, arenas, turn, s, cache, work, work2);
         settle(ctx, s, (long long)T * width_, false);
+        bool normed_ahead = false;          // `work` already holds the rows of the coming sub-layer's norm
         for (size_t i = 0; i < sublayers.size(); ++i) {
             const SubLayer& sub = sublayers[i];
             // this sub-layer's arena: what the sub-layer before the last one left there is dead by now
@@ -184,7 +185,10 @@ public:
             s.delta = Delta();
             PartInput in;
             in.rows = Rows{work, ctx.dtype, T, hidden, hidden};
-            if (sub.shift) {
+            if (normed_ahead) {
+                // the sub-layer in front left this norm's rows in `work` when its output joined the stream
+                normed_ahead = false;
+            } else if (sub.shift) {
                 // norm, then the mix with the row in front: one kernel where the norm is a plain RMSNorm, else the normed
                 // rows in float32 and the shift behind them
                 if (!cache.layer_state || cache.layer_state_floats < sub.shift->state_floats()) throw DeviceError("a shift was handed no state of its size");
@@ -203,10 +207,20 @@ public:
             }
             Delta d = sub.mixer ? sub.mixer->forward(ctx, in, cache, nullptr) : sub.feed_forward->forward(ctx, in, nullptr);
             if (d.has_pre()) throw DeviceError("a part returned prepared rows without having been offered the norm that follows");
-            if (sub.output_norm && !(sub.norm && sub.placement == "post") && sub.output_norm->add_normed(ctx, s.residual, d.p, d.dtype, T)) {
-                // the branch's output went into the stream through its norm, in float32, in one kernel
-                s.delta = Delta();
-                continue;
+            if (sub.output_norm && !(sub.norm && sub.placement == "post")) {
+                // the branch's output goes into the stream through its norm, in float32, in one kernel; where the next sub-layer
+                // starts with a plain norm of the same stream (no shift), that norm's rows come out of the same kernel
+                const SubLayer* next = i + 1 < sublayers.size() ? &sublayers[i + 1] : nullptr;
+                if (next && next->norm && next->placement == "pre" && !next->shift && !next->plain_pre_norm &&
+                    sub.output_norm->add_normed_then(ctx, s.residual, d.p, d.dtype, T, next->norm.get(), work, ctx.dtype)) {
+                    normed_ahead = true;
+                    s.delta = Delta();
+                    continue;
+                }
+                if (sub.output_norm->add_normed(ctx, s.residual, d.p, d.dtype, T)) {
+                    s.delta = Delta();
+                    continue;
+                }
             }
             if (sub.output_norm) {
                 // norm(delta) in the compute dtype: through the float32 spare buffer

@@ -210,6 +210,16 @@ public:
         launch_check(eg_rmsnorm_add(ctx.stream, residual, y, (int)y_dtype, size_, gain_.as<float>(), eps_, num_rows, size_), "rmsnorm_add");
         return true;
     }
+    bool add_normed_then(const StepContext& ctx, float* residual, const void* y, DType y_dtype, int num_rows, const Norm* next, void* out,
+                         DType out_dtype) const override {
+        const float* gain2 = nullptr;
+        float eps2 = 0.f;
+        if (!next || next->size() != size_ || !next->rms_parameters(&gain2, &eps2)) return false;
+        const int rc = eg_rmsnorm_add_norm(ctx.stream, residual, y, (int)y_dtype, size_, gain_.as<float>(), eps_, gain2, eps2, out, (int)out_dtype, num_rows, size_);
+        if (rc == (int)cudaErrorInvalidValue) return false;      // a size the fused kernel does not take
+        launch_check(rc, "rmsnorm_add_norm");
+        return true;
+    }
     int size() const override { return size_; }
 
 private:

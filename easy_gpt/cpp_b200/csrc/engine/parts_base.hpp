@@ -205,6 +205,11 @@ public:
     // residual[t] += this norm of y[t] (a branch's output joins the stream through its norm), in one kernel; false: this
     // norm cannot (the caller norms into a buffer and adds)
     virtual bool add_normed(const StepContext& /*ctx*/, float* /*residual*/, const void* /*y*/, DType /*y_dtype*/, int /*num_rows*/) const { return false; }
+    // the same and, from the new rows, `next`'s norm into out (the norm in front of the branch that follows), in one kernel
+    virtual bool add_normed_then(const StepContext& /*ctx*/, float* /*residual*/, const void* /*y*/, DType /*y_dtype*/, int /*num_rows*/, const Norm* /*next*/,
+                                 void* /*out*/, DType /*out_dtype*/) const {
+        return false;
+    }
     virtual int size() const = 0;
 };
 

@@ -201,7 +201,7 @@ public:
         int r = 0, l = 0;
         if (!eg_gated_delta_plan(dk_, dv_, &r, &l))
             throw std::invalid_argument("gated delta: dim " + std::to_string(dk_) + " with vdim " + std::to_string(dv_) +
-                                        " is beyond what the kernel takes (dim up to 64 with vdim up to 256, dim up to 256 with vdim up to 128)");
+                                        " is beyond what the kernel takes (dim up to 256, vdim up to 4096)");
     }
     int channels() const { return 2 * kv_heads_ * dk_ + heads_ * dv_; }
     std::vector<TensorRequest> tensor_requests() const override {
@@ -233,7 +233,7 @@ public:
     }
     size_t weight_bytes() const override { return in_.weight_bytes() + out_.weight_bytes() + (size_t)channels() * taps_ * 4; }
     size_t arena_bytes(long long T) const override {
-        return (size_t)T * ((size_t)in_.out_features * 4 + (size_t)channels() * 4 + (size_t)heads_ * dv_ * 8 + (size_t)hidden_ * 4) + (1u << 16);
+        return (size_t)T * ((size_t)in_.out_features * 4 + (size_t)channels() * 4 + (size_t)heads_ * dv_ * 8 + (size_t)heads_ * 16 + (size_t)hidden_ * 4) + (1u << 16);
     }
     bool capturable() const override { return true; }
     long long conv_floats() const { return (long long)(taps_ - 1) * channels(); }
@@ -259,9 +259,10 @@ public:
         // few (entry, head) pairs: a head's columns are dealt to several blocks (they do not depend on one another), and the
         // norm over a head's outputs becomes a kernel of its own.  The count depends on the step's size alone.
         const int slices = plans::delta_column_slices(ctx.num_seqs, heads_, dv_);
-        float* o_raw = slices > 1 ? ctx.take<float>((size_t)T * heads_ * dv_) : nullptr;
+        float* o_raw = ctx.take<float>((size_t)T * heads_ * dv_);                   // raw outputs, where no single block holds a head
+        float* aux = ctx.take<float>((size_t)T * heads_ * 4);                       // beta, g, k . q per token and head
         launch_check(eg_gated_delta(ctx.stream, u, C, 0, qk, 2 * qk, (const float*)proj.p, proj.ld, b_col, a_col, z_col, a_log_.as<float>(), dt_bias_.as<float>(),
-                                    norm_w_.as<float>(), state, slot, conv_floats(), ctx.seq_starts, ctx.seq_slots, y.p, (int)dtype, y.ld, o_raw, slices, T,
+                                    norm_w_.as<float>(), state, slot, conv_floats(), ctx.seq_starts, ctx.seq_slots, y.p, (int)dtype, y.ld, aux, o_raw, slices, T,
                                     ctx.num_seqs, heads_, kv_heads_, dk_, dv_, unit_eps_, eps_), "gated_delta");
         const Rows o = out_(ctx, y, /*out_f32=*/true);
         Delta d;

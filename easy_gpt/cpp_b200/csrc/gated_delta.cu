@@ -9,12 +9,17 @@
 // q, k, v are the convolved and activated projections (float32 [tokens, ...]), b, a and z columns of the projection's
 // float32 output.  Head h reads key head h / (heads / kv_heads).
 //
-// One block per (head, batch entry).  Column j of S belongs to P neighbouring lanes, each with R = ceil(dk / P) of its
-// rows in registers for the entry's whole run of tokens, so a token costs two dot products over the old S (with k^ and
-// with q^, independent of each other: o = g S_old^T q^ + u (k^ . q^)), a few shuffles and one update per element.  The
-// block walks the entry in tiles of tokens staged in shared memory, where it also norms the tile's queries and keys;
-// the tile's outputs are normed per head and gated before they leave.  The slot keeps S as [head, dv, dk], so that a
+// A kernel over all tokens first makes the unit vectors and the per-token numbers (beta, g, k^ . q^).  Then one block per
+// (head, batch entry, slice of the head's columns: the columns of S do not depend on one another).  Column j of S belongs
+// to P neighbouring lanes, each with R = ceil(dk / P) of its rows in registers for the entry's whole run of tokens, so a
+// token costs two dot products over the old S (with k^ and with q^, independent of each other: o = g S_old^T q^ +
+// u (k^ . q^)), a few shuffles and one update per element.  The block walks the entry in tiles of tokens that arrive in
+// shared memory by asynchronous copies, the next tile's behind this one's steps; outputs are normed per head and gated by
+// the block itself where it holds whole heads, else by a kernel behind.  The slot keeps S as [head, dv, dk], so that a
 // thread's rows are neighbours in memory.  The order of every sum depends on the sizes alone.
+#include <algorithm>
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace {
@@ -44,27 +49,69 @@ __device__ __forceinline__ float decay_exp(float x) {
 constexpr int TILE = 16;        // tokens staged at a time
 constexpr int PAD = 4;          // floats between the parts' rows of a staged key or query: the parts' 16-byte loads then hit different banks
 
+__device__ __forceinline__ void copy_async_16(float* smem_dst, const float* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void copy_async_4(float* smem_dst, const float* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(src) : "memory");
+}
+
+// Before the recurrence, for all tokens at once: a warp per (token, key head) makes the head's query and key unit vectors in
+// place (the query also times dk^(-1/2)) and leaves, for every head of its group, (beta, g, k^ . q^) in aux [tokens, heads, 4].
+__global__ void __launch_bounds__(128) delta_prepare_kernel(float* __restrict__ qkv, long long ldq, int q_col, int k_col, const float* __restrict__ proj,
+                                                            long long ldp, int b_col, int a_col, const float* __restrict__ a_log,
+                                                            const float* __restrict__ dt_bias, float* __restrict__ aux, int tokens, int heads,
+                                                            int kv_heads, int dk, float unit_eps) {
+    const int lane = threadIdx.x & 31;
+    const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (w >= (long long)tokens * kv_heads) return;
+    const int t = (int)(w / kv_heads), g = (int)(w % kv_heads);
+    float* q = qkv + (size_t)t * ldq + q_col + (size_t)g * dk;
+    float* k = qkv + (size_t)t * ldq + k_col + (size_t)g * dk;
+    float kk = 0.f, qq = 0.f, kq = 0.f;
+    for (int d = lane; d < dk; d += 32) {
+        const float a = k[d], b = q[d];
+        kk = fmaf(a, a, kk);
+        qq = fmaf(b, b, qq);
+        kq = fmaf(a, b, kq);
+    }
+    kk = warp_sum(kk);
+    qq = warp_sum(qq);
+    kq = warp_sum(kq);
+    const float ik = 1.0f / sqrtf(kk + unit_eps), iq = (1.0f / sqrtf((float)dk)) / sqrtf(qq + unit_eps);
+    for (int d = lane; d < dk; d += 32) {
+        k[d] *= ik;
+        q[d] *= iq;
+    }
+    const int per = heads / kv_heads;
+    const float* row = proj + (size_t)t * ldp;
+    for (int i = lane; i < per; i += 32) {
+        const int head = g * per + i;
+        float* out = aux + ((size_t)t * heads + head) * 4;
+        out[0] = 1.0f / (1.0f + expf(-row[b_col + head]));
+        out[1] = decay_exp(-expf(a_log[head]) * softplus_f(row[a_col + head] + dt_bias[head]));
+        out[2] = kq * ik * iq;
+        out[3] = 0.f;
+    }
+}
+
 // grid (heads, entries, column slices): a block holds `cols` columns of a head's S.  With o_raw the block leaves its columns
 // of o there (float32) and the norm over the head's columns is another kernel's; without, the block holds whole heads and
-// norms and gates its outputs itself.
+// norms and gates its outputs itself.  The tiles' keys, queries, values and (beta, g, k . q) come by asynchronous copies into
+// one of two buffers, the next tile's while this one's steps run.
 template <typename TO, int R, int P>
 __global__ void __launch_bounds__(1024) gated_delta_kernel(const float* __restrict__ qkv, long long ldq, int q_col, int k_col, int v_col,
-                                                           const float* __restrict__ proj, long long ldp, int b_col, int a_col, int z_col,
-                                                           const float* __restrict__ a_log, const float* __restrict__ dt_bias,
+                                                           const float* __restrict__ proj, long long ldp, int z_col, const float* __restrict__ aux,
                                                            const float* __restrict__ norm_w, float* __restrict__ state, long long slot_floats,
                                                            long long state_offset, const int* __restrict__ seq_starts,
                                                            const int* __restrict__ seq_slots, TO* __restrict__ y, long long ldy,
-                                                           float* __restrict__ o_raw, int cols, int heads, int kv_heads, int dk, int dv,
-                                                           float unit_eps, float eps) {
-    extern __shared__ float smem[];
+                                                           float* __restrict__ o_raw, int cols, int heads, int kv_heads, int dk, int dv, float eps,
+                                                           int wide) {
+    extern __shared__ __align__(16) float smem[];
     constexpr int RS = R + PAD, DKS = RS * P;       // a part's stride, a staged row's length (rows beyond dk hold zeros)
-    float* s_k = smem;                              // [TILE, DKS]
-    float* s_q = s_k + TILE * DKS;                  // [TILE, DKS]
-    float* s_v = s_q + TILE * DKS;                  // [TILE, cols]
-    float* s_o = s_v + TILE * cols;                 // [TILE, cols]
-    float* s_beta = s_o + TILE * cols;              // [TILE]
-    float* s_g = s_beta + TILE;
-    float* s_kq = s_g + TILE;
+    const int vcols = (cols + 3) & ~3;
+    const int stage_floats = TILE * (2 * DKS + vcols + 4);
+    float* s_o = smem + 2 * stage_floats;           // [TILE, cols]
     const int head = blockIdx.x, seq = blockIdx.y, j0 = blockIdx.z * cols;
     const int kvh = head / (heads / kv_heads);
     const int start = seq_starts[seq], count = seq_starts[seq + 1] - start;
@@ -79,50 +126,63 @@ __global__ void __launch_bounds__(1024) gated_delta_kernel(const float* __restri
         const int row = part * R + r;
         s[r] = (active && row < dk) ? S[row] : 0.f;
     }
-    const float rate = -expf(a_log[head]), bias = dt_bias[head], q_scale = 1.0f / sqrtf((float)dk);
-    for (int t0 = 0; t0 < count; t0 += TILE) {
-        const int n = min(TILE, count - t0);
-        __syncthreads();                            // the tile before is done with shared memory
-        for (int i = threadIdx.x; i < n * R * P; i += blockDim.x) {
-            const int t = i / (R * P), d = i % (R * P);
-            const float* row = qkv + (size_t)(start + t0 + t) * ldq;
-            const int at = t * DKS + (d / R) * RS + d % R;
-            s_k[at] = d < dk ? row[k_col + kvh * dk + d] : 0.f;
-            s_q[at] = d < dk ? row[q_col + kvh * dk + d] : 0.f;
-        }
-        for (int i = threadIdx.x; i < n * width; i += blockDim.x) {
-            const int t = i / width, d = i % width;
-            s_v[t * cols + d] = qkv[(size_t)(start + t0 + t) * ldq + v_col + head * dv + j0 + d];
-        }
-        if (threadIdx.x < n) {
-            const float* row = proj + (size_t)(start + t0 + threadIdx.x) * ldp;
-            s_beta[threadIdx.x] = 1.0f / (1.0f + expf(-row[b_col + head]));
-            s_g[threadIdx.x] = decay_exp(rate * softplus_f(row[a_col + head] + bias));
-        }
-        __syncthreads();
-        // unit keys and queries, and k^ . q^, a warp per token
-        for (int t = warp; t < n; t += warps) {
-            float kk = 0.f, qq = 0.f, kq = 0.f;
-            for (int d = lane; d < R * P; d += 32) {
+    for (int i = threadIdx.x; i < 2 * stage_floats; i += blockDim.x) smem[i] = 0.f;      // rows beyond dk stay zero
+    __syncthreads();
+    // tile `ti` into buffer `b`: 16-byte pieces where every row starts on a 16-byte boundary (wide), else value by value
+    auto fetch = [&](int ti, int b) {
+        const int t0 = ti * TILE, n = min(TILE, count - t0);
+        float* sk = smem + b * stage_floats;
+        float* sq = sk + TILE * DKS;
+        float* sv = sq + TILE * DKS;
+        float* sa = sv + TILE * vcols;
+        if (wide) {
+            const int pieces = dk / 4;
+            for (int i = threadIdx.x; i < n * pieces; i += blockDim.x) {
+                const int t = i / pieces, d = (i % pieces) * 4;
+                const float* row = qkv + (size_t)(start + t0 + t) * ldq;
                 const int at = t * DKS + (d / R) * RS + d % R;
-                const float a = s_k[at], b = s_q[at];
-                kk = fmaf(a, a, kk);
-                qq = fmaf(b, b, qq);
-                kq = fmaf(a, b, kq);
+                copy_async_16(sk + at, row + k_col + kvh * dk + d);
+                copy_async_16(sq + at, row + q_col + kvh * dk + d);
             }
-            kk = warp_sum(kk);
-            qq = warp_sum(qq);
-            kq = warp_sum(kq);
-            const float ik = 1.0f / sqrtf(kk + unit_eps), iq = q_scale / sqrtf(qq + unit_eps);
-            for (int d = lane; d < R * P; d += 32) {
+            const int vp = width / 4;
+            for (int i = threadIdx.x; i < n * vp; i += blockDim.x) {
+                const int t = i / vp, d = (i % vp) * 4;
+                copy_async_16(sv + t * vcols + d, qkv + (size_t)(start + t0 + t) * ldq + v_col + head * dv + j0 + d);
+            }
+            for (int t = threadIdx.x; t < n; t += blockDim.x) copy_async_16(sa + t * 4, aux + ((size_t)(start + t0 + t) * heads + head) * 4);
+        } else {
+            for (int i = threadIdx.x; i < n * dk; i += blockDim.x) {
+                const int t = i / dk, d = i % dk;
+                const float* row = qkv + (size_t)(start + t0 + t) * ldq;
                 const int at = t * DKS + (d / R) * RS + d % R;
-                s_k[at] *= ik;
-                s_q[at] *= iq;
+                copy_async_4(sk + at, row + k_col + kvh * dk + d);
+                copy_async_4(sq + at, row + q_col + kvh * dk + d);
             }
-            if (lane == 0) s_kq[t] = kq * ik * iq;
+            for (int i = threadIdx.x; i < n * width; i += blockDim.x) {
+                const int t = i / width, d = i % width;
+                copy_async_4(sv + t * vcols + d, qkv + (size_t)(start + t0 + t) * ldq + v_col + head * dv + j0 + d);
+            }
+            for (int i = threadIdx.x; i < n * 3; i += blockDim.x)
+                copy_async_4(sa + (i / 3) * 4 + i % 3, aux + ((size_t)(start + t0 + i / 3) * heads + head) * 4 + i % 3);
         }
-        __syncthreads();
-        for (int t = 0; t < n; ++t) {
+        asm volatile("cp.async.commit_group;\n" ::: "memory");
+    };
+    const int tiles = (count + TILE - 1) / TILE;
+    if (tiles > 0) fetch(0, 0);
+    for (int ti = 0; ti < tiles; ++ti) {
+        const int t0 = ti * TILE, n = min(TILE, count - t0);
+        if (ti + 1 < tiles) {
+            fetch(ti + 1, (ti + 1) & 1);
+            asm volatile("cp.async.wait_group 1;\n" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+        }
+        __syncthreads();                            // this tile has arrived; the tile before is done with s_o
+        const float* s_k = smem + (ti & 1) * stage_floats;
+        const float* s_q = s_k + TILE * DKS;
+        const float* s_v = s_q + TILE * DKS;
+        const float* s_a = s_v + TILE * vcols;
+        auto step = [&](int t) {
             const float4* kt = reinterpret_cast<const float4*>(s_k + t * DKS + part * RS);
             const float4* qt = reinterpret_cast<const float4*>(s_q + t * DKS + part * RS);
             float kv[R];
@@ -140,13 +200,20 @@ __global__ void __launch_bounds__(1024) gated_delta_kernel(const float* __restri
                 sk += __shfl_xor_sync(0xffffffffu, sk, o);
                 sq += __shfl_xor_sync(0xffffffffu, sq, o);
             }
-            const float g = s_g[t];
-            const float u = s_beta[t] * ((active ? s_v[t * cols + jl] : 0.f) - g * sk);
+            const float4 bgk = *reinterpret_cast<const float4*>(s_a + t * 4);      // beta, g, k . q
+            const float g = bgk.y;
+            const float u = bgk.x * ((active ? s_v[t * vcols + jl] : 0.f) - g * sk);
 #pragma unroll
             for (int r = 0; r < R; ++r) s[r] = fmaf(kv[r], u, g * s[r]);
-            if (active && part == 0) s_o[t * cols + jl] = fmaf(g, sq, u * s_kq[t]);
+            if (active && part == 0) s_o[t * cols + jl] = fmaf(g, sq, u * bgk.z);
+        };
+        if (n == TILE) {                            // a whole tile: unrolled, so that the loads of the next tokens go out ahead of their steps
+#pragma unroll 4
+            for (int t = 0; t < TILE; ++t) step(t);
+        } else {
+            for (int t = 0; t < n; ++t) step(t);
         }
-        __syncthreads();
+        __syncthreads();                            // the tile's outputs are complete; its buffer may be filled again
         if (o_raw) {
             for (int i = threadIdx.x; i < n * width; i += blockDim.x) {
                 const int t = i / width, d = i % width;
@@ -193,27 +260,37 @@ __global__ void delta_output_kernel(const float* __restrict__ o_raw, const float
 }
 
 template <typename TO, int R, int P>
-int launch_delta(cudaStream_t stream, const float* qkv, long long ldq, int q_col, int k_col, int v_col, const float* proj, long long ldp, int b_col,
+int launch_delta(cudaStream_t stream, float* qkv, long long ldq, int q_col, int k_col, int v_col, const float* proj, long long ldp, int b_col,
                  int a_col, int z_col, const float* a_log, const float* dt_bias, const float* norm_w, float* state, long long slot_floats,
-                 long long state_offset, const int* seq_starts, const int* seq_slots, void* y, long long ldy, float* o_raw, int slices, int tokens,
-                 int num_seqs, int heads, int kv_heads, int dk, int dv, float unit_eps, float eps) {
-    // columns per block: whole warps of them (32 / P columns a warp)
-    const int per_warp = 32 / P;
+                 long long state_offset, const int* seq_starts, const int* seq_slots, void* y, long long ldy, float* aux, float* o_raw, int slices,
+                 int tokens, int num_seqs, int heads, int kv_heads, int dk, int dv, float unit_eps, float eps) {
+    // columns per block: whole warps of them (32 / P columns a warp), and a multiple of four so that the slices' values start on 16-byte boundaries
+    const int per_warp = 32 / P < 4 ? 4 : 32 / P;
+    const int most_cols = 1024 / P / per_warp * per_warp;       // a block has at most 1024 threads
+    if (!o_raw) slices = 1;
     int cols = (dv + slices - 1) / slices;
-    cols = (cols + per_warp - 1) / per_warp * per_warp;
-    if (!o_raw) cols = (dv + per_warp - 1) / per_warp * per_warp;
-    slices = o_raw ? (dv + cols - 1) / cols : 1;
+    cols = std::min((cols + per_warp - 1) / per_warp * per_warp, most_cols);
+    slices = (dv + cols - 1) / cols;
+    if (slices > 1 && !o_raw) return (int)cudaErrorInvalidValue;  // a head that no single block holds needs the buffer for its raw outputs
+    if (slices == 1) o_raw = nullptr;
     const int threads = cols * P;
-    const size_t smem = ((size_t)TILE * (2 * (R + PAD) * P + 2 * cols) + 3 * TILE) * sizeof(float);
+    const int vcols = (cols + 3) & ~3;
+    const size_t smem = ((size_t)2 * TILE * (2 * (R + PAD) * P + vcols + 4) + (size_t)TILE * cols) * sizeof(float);
     if (threads > 1024 || smem > 200 * 1024) return (int)cudaErrorInvalidValue;
     auto kernel = gated_delta_kernel<TO, R, P>;
     if (smem > 48 * 1024) {
         const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
     }
-    kernel<<<dim3(heads, num_seqs, slices), threads, smem, stream>>>(qkv, ldq, q_col, k_col, v_col, proj, ldp, b_col, a_col, z_col, a_log, dt_bias, norm_w,
-                                                                     state, slot_floats, state_offset, seq_starts, seq_slots, (TO*)y, ldy, o_raw, cols, heads,
-                                                                     kv_heads, dk, dv, unit_eps, eps);
+    const long long prep = (long long)tokens * kv_heads;
+    delta_prepare_kernel<<<(unsigned)((prep + 3) / 4), 128, 0, stream>>>(qkv, ldq, q_col, k_col, proj, ldp, b_col, a_col, a_log, dt_bias, aux, tokens, heads,
+                                                                         kv_heads, dk, unit_eps);
+    // 16-byte copies need every copied row to start on a 16-byte boundary
+    const int wide = dk % 4 == 0 && dv % 4 == 0 && ldq % 4 == 0 && q_col % 4 == 0 && k_col % 4 == 0 && v_col % 4 == 0 && (uintptr_t)qkv % 16 == 0 &&
+                     (uintptr_t)aux % 16 == 0;
+    kernel<<<dim3(heads, num_seqs, slices), threads, smem, stream>>>(qkv, ldq, q_col, k_col, v_col, proj, ldp, z_col, aux, norm_w, state, slot_floats,
+                                                                     state_offset, seq_starts, seq_slots, (TO*)y, ldy, o_raw, cols, heads, kv_heads, dk, dv,
+                                                                     eps, wide);
     if (o_raw) {
         const long long warps = (long long)tokens * heads;
         delta_output_kernel<TO><<<(unsigned)((warps + 3) / 4), 128, 0, stream>>>(o_raw, proj, ldp, z_col, norm_w, (TO*)y, ldy, tokens, heads, dv, eps);
@@ -222,53 +299,59 @@ int launch_delta(cudaStream_t stream, const float* qkv, long long ldq, int q_col
 }
 
 template <typename TO>
-int dispatch_delta(int R, int P, cudaStream_t stream, const float* qkv, long long ldq, int q_col, int k_col, int v_col, const float* proj, long long ldp,
+int dispatch_delta(int R, int P, cudaStream_t stream, float* qkv, long long ldq, int q_col, int k_col, int v_col, const float* proj, long long ldp,
                    int b_col, int a_col, int z_col, const float* a_log, const float* dt_bias, const float* norm_w, float* state, long long slot_floats,
-                   long long state_offset, const int* seq_starts, const int* seq_slots, void* y, long long ldy, float* o_raw, int slices, int tokens,
-                   int num_seqs, int heads, int kv_heads, int dk, int dv, float unit_eps, float eps) {
+                   long long state_offset, const int* seq_starts, const int* seq_slots, void* y, long long ldy, float* aux, float* o_raw, int slices,
+                   int tokens, int num_seqs, int heads, int kv_heads, int dk, int dv, float unit_eps, float eps) {
 #define EG_DELTA(RR, PP)                                                                                                                                  \
     if (R == RR && P == PP)                                                                                                                               \
         return launch_delta<TO, RR, PP>(stream, qkv, ldq, q_col, k_col, v_col, proj, ldp, b_col, a_col, z_col, a_log, dt_bias, norm_w, state, slot_floats, \
-                                        state_offset, seq_starts, seq_slots, y, ldy, o_raw, slices, tokens, num_seqs, heads, kv_heads, dk, dv, unit_eps, eps)
+                                        state_offset, seq_starts, seq_slots, y, ldy, aux, o_raw, slices, tokens, num_seqs, heads, kv_heads, dk, dv, unit_eps, \
+                                        eps)
     EG_DELTA(4, 4);
     EG_DELTA(8, 4);
-    EG_DELTA(16, 4);
-    EG_DELTA(16, 8);
-    EG_DELTA(32, 8);
+    EG_DELTA(8, 8);
+    EG_DELTA(8, 16);
+    EG_DELTA(8, 32);
+    EG_DELTA(4, 16);
+    EG_DELTA(4, 32);
 #undef EG_DELTA
     return (int)cudaErrorInvalidValue;
 }
 }  // namespace
 
 // How a head's rows are spread for these sizes: P lanes a column with R rows each (R * P >= dk); 0 if the kernel does
-// not take the sizes (a block holds a whole head: dv * P threads, at most 1024).
+// not take the sizes.  Few rows a lane and many lanes a column: a token's work is a chain of dependent steps, and a
+// scheduler hides one warp's waits only behind other warps (measured on B200 with 128 x 128 states, 2,048 tokens: 16 rows
+// a lane, 512 warps in all, 640 cycles a token, of which 92% waits).
 EG_API int eg_gated_delta_plan(int dk, int dv, int* rows_per_lane, int* lanes) {
-    if (dk <= 0 || dv <= 0 || dk > 256) return 0;
-    const int P = dk > 64 ? 8 : 4;
-    if (dv * P > 1024) return 0;
-    int R = P == 8 ? 16 : 4;
-    while (R * P < dk) R *= 2;
-    *rows_per_lane = R;
-    *lanes = P;
+    if (dk <= 0 || dv <= 0 || dk > 256 || dv > 4096) return 0;
+    *rows_per_lane = dk <= 16 ? 4 : 8;
+    *lanes = dk <= 32 ? 4 : dk <= 64 ? 8 : dk <= 128 ? 16 : 32;
+    static const int few = getenv("EASY_GPT_DELTA_ROWS") ? atoi(getenv("EASY_GPT_DELTA_ROWS")) : 0;      // for measurements: 4 rows a lane
+    if (few == 4 && dk > 32 && dk <= 128) {
+        *rows_per_lane = 4;
+        *lanes = dk <= 64 ? 16 : 32;
+    }
     return 1;
 }
 
 // qkv float32 [tokens, ldq]: convolved, activated queries (key heads x dk at q_col), keys (k_col) and values (heads x dv at
-// v_col).  proj float32 [tokens, ldp]: the projection's output with b (heads) at b_col, a (heads) at a_col and the output
-// gate z (heads x dv) at z_col.  state: the requests' slots; S of a request lies state_offset floats into its slot, as
-// [heads, dv, dk].  y [tokens, ldy] in y_dtype.  slices > 1 (with o_raw, float32 [tokens, heads * dv]): a head's columns
-// are dealt to that many blocks, for steps with few (entry, head) pairs, and the outputs are normed by a second kernel.
-EG_API int eg_gated_delta(cudaStream_t stream, const float* qkv, long long ldq, int q_col, int k_col, int v_col, const float* proj, long long ldp,
-                          int b_col, int a_col, int z_col, const float* a_log, const float* dt_bias, const float* norm_w, float* state,
-                          long long slot_floats, long long state_offset, const int* seq_starts, const int* seq_slots, void* y, int y_dtype, long long ldy,
+// v_col); queries and keys are made unit vectors in place.  proj float32 [tokens, ldp]: the projection's output with b
+// (heads) at b_col, a (heads) at a_col and the output gate z (heads x dv) at z_col.  aux: float32 [tokens, heads, 4] of
+// scratch.  state: the requests' slots; S of a request lies state_offset floats into its slot, as [heads, dv, dk].
+// y [tokens, ldy] in y_dtype.  slices > 1 (with o_raw, float32 [tokens, heads * dv]): a head's columns are dealt to that
+// many blocks, for steps with few (entry, head) pairs, and the outputs are normed by a kernel behind.
+EG_API int eg_gated_delta(cudaStream_t stream, float* qkv, long long ldq, int q_col, int k_col, int v_col, const float* proj, long long ldp, int b_col,
+                          int a_col, int z_col, const float* a_log, const float* dt_bias, const float* norm_w, float* state, long long slot_floats,
+                          long long state_offset, const int* seq_starts, const int* seq_slots, void* y, int y_dtype, long long ldy, float* aux,
                           float* o_raw, int slices, int tokens, int num_seqs, int heads, int kv_heads, int dk, int dv, float unit_eps, float eps) {
-    if (num_seqs <= 0) return 0;
+    if (num_seqs <= 0 || tokens <= 0) return 0;
     int R = 0, P = 0;
-    if (kv_heads <= 0 || heads % kv_heads || !eg_gated_delta_plan(dk, dv, &R, &P) || slices < 1) return (int)cudaErrorInvalidValue;
-    if (slices == 1 || !o_raw) { o_raw = nullptr; slices = 1; }
+    if (kv_heads <= 0 || heads % kv_heads || !eg_gated_delta_plan(dk, dv, &R, &P) || slices < 1 || !aux) return (int)cudaErrorInvalidValue;
     if (y_dtype == EG_BF16)
         return dispatch_delta<bf16>(R, P, stream, qkv, ldq, q_col, k_col, v_col, proj, ldp, b_col, a_col, z_col, a_log, dt_bias, norm_w, state, slot_floats,
-                                    state_offset, seq_starts, seq_slots, y, ldy, o_raw, slices, tokens, num_seqs, heads, kv_heads, dk, dv, unit_eps, eps);
+                                    state_offset, seq_starts, seq_slots, y, ldy, aux, o_raw, slices, tokens, num_seqs, heads, kv_heads, dk, dv, unit_eps, eps);
     return dispatch_delta<float>(R, P, stream, qkv, ldq, q_col, k_col, v_col, proj, ldp, b_col, a_col, z_col, a_log, dt_bias, norm_w, state, slot_floats,
-                                 state_offset, seq_starts, seq_slots, y, ldy, o_raw, slices, tokens, num_seqs, heads, kv_heads, dk, dv, unit_eps, eps);
+                                 state_offset, seq_starts, seq_slots, y, ldy, aux, o_raw, slices, tokens, num_seqs, heads, kv_heads, dk, dv, unit_eps, eps);
 }

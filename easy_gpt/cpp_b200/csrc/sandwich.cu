@@ -79,6 +79,153 @@ __global__ void rmsnorm_add_kernel(float* __restrict__ stream, const TD* __restr
     for (int j = threadIdx.x; j < hidden; j += blockDim.x) x[j] += gain[j] * (to_f32<TD>(row[j]) * inv);
 }
 
+// ---- rows of up to 4096 (norm and add) or 2048 (norm and shift) values that are a multiple of 4 wide: a warp per row, the
+// row in registers (VPL float4 a lane), so that it is read once with all of its loads in flight, and the sum is a shuffle.
+// The sum's order (a lane's values in order, then the lanes by halving) depends on the width alone.
+__device__ __forceinline__ float4 load4(const float* p, int q) { return reinterpret_cast<const float4*>(p)[q]; }
+__device__ __forceinline__ float4 load4(const bf16* p, int q) {
+    const uint2 raw = reinterpret_cast<const uint2*>(p)[q];
+    const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&raw.x), b = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+    return make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
+}
+__device__ __forceinline__ void store4(float* p, int q, float4 v) { reinterpret_cast<float4*>(p)[q] = v; }
+__device__ __forceinline__ void store4(bf16* p, int q, float4 v) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+    uint2 packed;
+    packed.x = *reinterpret_cast<uint32_t*>(&lo);
+    packed.y = *reinterpret_cast<uint32_t*>(&hi);
+    reinterpret_cast<uint2*>(p)[q] = packed;
+}
+__device__ __forceinline__ float squares(float4 v) { return v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w; }
+
+template <typename TD, int VPL>
+__global__ void __launch_bounds__(256) rmsnorm_add_warp_kernel(float* __restrict__ stream, const TD* __restrict__ y, long long ldy,
+                                                               const float* __restrict__ gain, float eps, int tokens, int hidden) {
+    const int lane = threadIdx.x & 31;
+    const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (t >= tokens) return;
+    const int quads = hidden / 4;
+    const TD* row = y + (size_t)t * ldy;
+    float* x = stream + (size_t)t * hidden;
+    float4 v[VPL], r[VPL];
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+        const int q = i * 32 + lane;
+        v[i] = q < quads ? load4(row, q) : make_float4(0.f, 0.f, 0.f, 0.f);
+        r[i] = q < quads ? load4(x, q) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) ss += squares(v[i]);
+    ss = warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss / (float)hidden + eps);
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+        const int q = i * 32 + lane;
+        if (q >= quads) continue;
+        const float4 g = load4(gain, q);
+        store4(x, q, make_float4(r[i].x + g.x * (v[i].x * inv), r[i].y + g.y * (v[i].y * inv), r[i].z + g.z * (v[i].z * inv), r[i].w + g.w * (v[i].w * inv)));
+    }
+}
+
+// x[t] += gain * y[t] / rms(y[t]), then out[t] = gain2 * x[t] / rms(x[t]): a branch joins the stream through its norm and the
+// norm in front of the next branch follows from the row in registers
+template <typename TD, typename TO, int VPL>
+__global__ void __launch_bounds__(256) rmsnorm_add_norm_warp_kernel(float* __restrict__ stream, const TD* __restrict__ y, long long ldy,
+                                                                    const float* __restrict__ gain, float eps, const float* __restrict__ gain2,
+                                                                    float eps2, TO* __restrict__ out, int tokens, int hidden) {
+    const int lane = threadIdx.x & 31;
+    const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (t >= tokens) return;
+    const int quads = hidden / 4;
+    const TD* row = y + (size_t)t * ldy;
+    float* x = stream + (size_t)t * hidden;
+    float4 v[VPL], r[VPL];
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+        const int q = i * 32 + lane;
+        v[i] = q < quads ? load4(row, q) : make_float4(0.f, 0.f, 0.f, 0.f);
+        r[i] = q < quads ? load4(x, q) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) ss += squares(v[i]);
+    ss = warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss / (float)hidden + eps);
+    float s2 = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+        const int q = i * 32 + lane;
+        if (q >= quads) continue;
+        const float4 g = load4(gain, q);
+        r[i] = make_float4(r[i].x + g.x * (v[i].x * inv), r[i].y + g.y * (v[i].y * inv), r[i].z + g.z * (v[i].z * inv), r[i].w + g.w * (v[i].w * inv));
+        store4(x, q, r[i]);
+        s2 += squares(r[i]);
+    }
+    s2 = warp_sum(s2);
+    const float inv2 = 1.0f / sqrtf(s2 / (float)hidden + eps2);
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+        const int q = i * 32 + lane;
+        if (q >= quads) continue;
+        const float4 g = load4(gain2, q);
+        store4(out + (size_t)t * hidden, q, make_float4(g.x * (r[i].x * inv2), g.y * (r[i].y * inv2), g.z * (r[i].z * inv2), g.w * (r[i].w * inv2)));
+    }
+}
+
+template <typename TO, int VPL>
+__global__ void __launch_bounds__(256) rmsnorm_shift_warp_kernel(const float* __restrict__ stream, const float* __restrict__ gain, float eps,
+                                                                 const float* __restrict__ mu, float* __restrict__ state, long long slot_floats,
+                                                                 const int* __restrict__ token_seq, const int* __restrict__ seq_starts,
+                                                                 const int* __restrict__ seq_slots, TO* __restrict__ out, int tokens, int hidden) {
+    const int lane = threadIdx.x & 31;
+    const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (t >= tokens) return;
+    const int quads = hidden / 4;
+    const int seq = token_seq[t], start = seq_starts[seq];
+    const bool first = t == start;
+    float* slot = state + (size_t)seq_slots[seq] * slot_floats;
+    const float* x = stream + (size_t)t * hidden;
+    // the row in front, normed again here; the first token's warp norms the entry's last row for the slot instead
+    const float* other = stream + (size_t)(first ? seq_starts[seq + 1] - 1 : t - 1) * hidden;
+    // the own row stays in registers; the other one is read twice (the second time from the cache), so that a warp holds
+    // one row and many warps fit an SM
+    float4 v[VPL];
+    float ss = 0.f, so = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+        const int q = i * 32 + lane;
+        v[i] = q < quads ? load4(x, q) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+        const int q = i * 32 + lane;
+        ss += squares(v[i]);
+        if (q < quads) so += squares(load4(other, q));
+    }
+    ss = warp_sum(ss);
+    so = warp_sum(so);
+    const float inv = 1.0f / sqrtf(ss / (float)hidden + eps), inv_other = 1.0f / sqrtf(so / (float)hidden + eps);
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+        const int q = i * 32 + lane;
+        if (q >= quads) continue;
+        const float4 g = load4(gain, q), m = load4(mu, q), o = load4(other, q);
+        const float4 a = make_float4(g.x * (v[i].x * inv), g.y * (v[i].y * inv), g.z * (v[i].z * inv), g.w * (v[i].w * inv));
+        const float4 b = make_float4(g.x * (o.x * inv_other), g.y * (o.y * inv_other), g.z * (o.z * inv_other), g.w * (o.w * inv_other));
+        const float4 p = first ? load4(slot, q) : b;
+        store4(out + (size_t)t * hidden, q, make_float4(fmaf(p.x - a.x, m.x, a.x), fmaf(p.y - a.y, m.y, a.y), fmaf(p.z - a.z, m.z, a.z), fmaf(p.w - a.w, m.w, a.w)));
+        if (first) store4(slot, q, b);
+    }
+}
+
+inline bool aligned16(const void* p) { return (uintptr_t)p % 16 == 0; }
+inline void warp_rows_launch(int rows, int* blocks, int* threads) {
+    const int warps = rows >= 2048 ? 8 : rows >= 512 ? 2 : 1;      // few rows: a warp a block, so that they are spread over the SMs
+    *blocks = (rows + warps - 1) / warps;
+    *threads = warps * 32;
+}
+
 __device__ __forceinline__ float xielu_f(float z, float ap, float an) {
     if (z > 0.f) return fmaf(ap * z, z, 0.5f * z);
     return fmaf(an, expm1f(z) - z, 0.5f * z);
@@ -137,6 +284,26 @@ EG_API int eg_rmsnorm_shift(cudaStream_t stream, const float* residual, const fl
                             long long slot_floats, const int* token_seq, const int* seq_starts, const int* seq_slots, void* out, int out_dtype,
                             int tokens, int hidden) {
     if (tokens <= 0) return 0;
+    // (few rows: a block a row spreads a row's loads over more threads; measured at 8 rows of 2,048: 8 us against 18)
+    if (tokens >= 256 && hidden % 4 == 0 && hidden <= 2048 && slot_floats % 4 == 0 && aligned16(residual) && aligned16(gain) && aligned16(mu) && aligned16(state) &&
+        aligned16(out)) {
+        int blocks, nt;
+        warp_rows_launch(tokens, &blocks, &nt);
+        const int vpl = (hidden / 4 + 31) / 32;
+#define EG_SHIFT_WARP(TO, V) \
+    rmsnorm_shift_warp_kernel<TO, V><<<blocks, nt, 0, stream>>>(residual, gain, eps, mu, state, slot_floats, token_seq, seq_starts, seq_slots, (TO*)out, tokens, hidden)
+        if (out_dtype == EG_BF16) {
+            if (vpl <= 4) EG_SHIFT_WARP(bf16, 4);
+            else if (vpl <= 8) EG_SHIFT_WARP(bf16, 8);
+            else EG_SHIFT_WARP(bf16, 16);
+        } else {
+            if (vpl <= 4) EG_SHIFT_WARP(float, 4);
+            else if (vpl <= 8) EG_SHIFT_WARP(float, 8);
+            else EG_SHIFT_WARP(float, 16);
+        }
+#undef EG_SHIFT_WARP
+        return eg_launch_status();
+    }
     const int threads = row_threads(hidden);
     if (out_dtype == EG_BF16)
         rmsnorm_shift_kernel<bf16><<<tokens, threads, 0, stream>>>(residual, gain, eps, mu, state, slot_floats, token_seq, seq_starts, seq_slots, (bf16*)out,
@@ -151,9 +318,53 @@ EG_API int eg_rmsnorm_shift(cudaStream_t stream, const float* residual, const fl
 EG_API int eg_rmsnorm_add(cudaStream_t stream, float* residual, const void* y, int y_dtype, long long ldy, const float* gain, float eps, int tokens,
                           int hidden) {
     if (tokens <= 0) return 0;
+    if (hidden % 4 == 0 && hidden <= 4096 && ldy % 4 == 0 && aligned16(residual) && aligned16(y) && aligned16(gain)) {
+        int blocks, nt;
+        warp_rows_launch(tokens, &blocks, &nt);
+        const int vpl = (hidden / 4 + 31) / 32;
+#define EG_ADD_WARP(TD, V) rmsnorm_add_warp_kernel<TD, V><<<blocks, nt, 0, stream>>>(residual, (const TD*)y, ldy, gain, eps, tokens, hidden)
+        if (y_dtype == EG_BF16) {
+            if (vpl <= 4) EG_ADD_WARP(bf16, 4);
+            else if (vpl <= 8) EG_ADD_WARP(bf16, 8);
+            else if (vpl <= 16) EG_ADD_WARP(bf16, 16);
+            else EG_ADD_WARP(bf16, 32);
+        } else {
+            if (vpl <= 4) EG_ADD_WARP(float, 4);
+            else if (vpl <= 8) EG_ADD_WARP(float, 8);
+            else if (vpl <= 16) EG_ADD_WARP(float, 16);
+            else EG_ADD_WARP(float, 32);
+        }
+#undef EG_ADD_WARP
+        return eg_launch_status();
+    }
     const int threads = row_threads(hidden);
     if (y_dtype == EG_BF16) rmsnorm_add_kernel<bf16><<<tokens, threads, 0, stream>>>(residual, (const bf16*)y, ldy, gain, eps, hidden);
     else rmsnorm_add_kernel<float><<<tokens, threads, 0, stream>>>(residual, (const float*)y, ldy, gain, eps, hidden);
+    return eg_launch_status();
+}
+
+// residual[t] += gain * y[t] / rms(y[t]), then out[t] = gain2 * residual[t] / rms(residual[t]) (eps2), in one kernel.  Returns
+// cudaErrorInvalidValue for sizes it does not take (rows of up to 2,048 values, a multiple of 4, 16-byte aligned).
+EG_API int eg_rmsnorm_add_norm(cudaStream_t stream, float* residual, const void* y, int y_dtype, long long ldy, const float* gain, float eps,
+                               const float* gain2, float eps2, void* out, int out_dtype, int tokens, int hidden) {
+    if (tokens <= 0) return 0;
+    if (hidden % 4 || hidden > 2048 || ldy % 4 || !aligned16(residual) || !aligned16(y) || !aligned16(gain) || !aligned16(gain2) || !aligned16(out))
+        return (int)cudaErrorInvalidValue;
+    int blocks, nt;
+    warp_rows_launch(tokens, &blocks, &nt);
+    const int vpl = (hidden / 4 + 31) / 32;
+#define EG_ADD_NORM(TD, TO, V) \
+    rmsnorm_add_norm_warp_kernel<TD, TO, V><<<blocks, nt, 0, stream>>>(residual, (const TD*)y, ldy, gain, eps, gain2, eps2, (TO*)out, tokens, hidden)
+#define EG_ADD_NORM_V(TD, TO)               \
+    if (vpl <= 4) EG_ADD_NORM(TD, TO, 4);   \
+    else if (vpl <= 8) EG_ADD_NORM(TD, TO, 8); \
+    else EG_ADD_NORM(TD, TO, 16)
+    if (y_dtype == EG_BF16 && out_dtype == EG_BF16) { EG_ADD_NORM_V(bf16, bf16); }
+    else if (y_dtype == EG_BF16) { EG_ADD_NORM_V(bf16, float); }
+    else if (out_dtype == EG_BF16) { EG_ADD_NORM_V(float, bf16); }
+    else { EG_ADD_NORM_V(float, float); }
+#undef EG_ADD_NORM_V
+#undef EG_ADD_NORM
     return eg_launch_status();
 }
 

@@ -68,6 +68,33 @@ __global__ void conv_silu_kernel(const T* __restrict__ x, long long ldx, const f
     u[(size_t)t * ldu + c] = from_f32<T>(silu_f(acc));
 }
 
+// float32 rows whose channels come in fours on 16-byte boundaries: a thread takes four channels of a token, every tap one
+// 16-byte load; the sums run over the taps in the same order as above
+__global__ void conv_silu_vec4_kernel(const float* __restrict__ x, long long ldx, const float* __restrict__ cw, const float* __restrict__ cb,
+                                      const float* __restrict__ state, long long slot_floats, const int* __restrict__ token_seq,
+                                      const int* __restrict__ seq_starts, const int* __restrict__ seq_slots, float* __restrict__ u, long long ldu,
+                                      int tokens, int channels, int taps) {
+    const int quads = channels / 4;
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long long)tokens * quads) return;
+    const int t = (int)(i / quads), c = (int)(i % quads) * 4;
+    const int seq = token_seq[t], start = seq_starts[seq];
+    const float* past = state + (size_t)seq_slots[seq] * slot_floats;
+    float acc[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) acc[e] = cb ? cb[c + e] : 0.0f;
+    for (int j = 0; j < taps; ++j) {
+        const int src = t - (taps - 1) + j;
+        const float4 v = src >= start ? *reinterpret_cast<const float4*>(x + (size_t)src * ldx + c)
+                                      : *reinterpret_cast<const float4*>(past + (size_t)(taps - 1 + src - start) * channels + c);
+        acc[0] = fmaf(cw[(size_t)c * taps + j], v.x, acc[0]);
+        acc[1] = fmaf(cw[(size_t)(c + 1) * taps + j], v.y, acc[1]);
+        acc[2] = fmaf(cw[(size_t)(c + 2) * taps + j], v.z, acc[2]);
+        acc[3] = fmaf(cw[(size_t)(c + 3) * taps + j], v.w, acc[3]);
+    }
+    *reinterpret_cast<float4*>(u + (size_t)t * ldu + c) = make_float4(silu_f(acc[0]), silu_f(acc[1]), silu_f(acc[2]), silu_f(acc[3]));
+}
+
 // one thread per (entry, channel): the slot's rows become the last taps-1 inputs of the request after this step
 template <typename T>
 __global__ void conv_state_kernel(const T* __restrict__ x, long long ldx, float* __restrict__ state, long long slot_floats,
@@ -251,6 +278,12 @@ EG_API int eg_conv_silu(cudaStream_t stream, int dtype, const void* x, long long
     const long long n = (long long)tokens * channels;
     if (n <= 0) return 0;
     if (taps < 1) return (int)cudaErrorInvalidValue;
+    if (dtype == EG_F32 && channels % 4 == 0 && ldx % 4 == 0 && ldu % 4 == 0 && slot_floats % 4 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)u % 16 == 0 &&
+        (uintptr_t)state % 16 == 0) {
+        conv_silu_vec4_kernel<<<(unsigned)((n / 4 + 255) / 256), 256, 0, stream>>>((const float*)x, ldx, conv_w, conv_b, state, slot_floats, token_seq,
+                                                                                 seq_starts, seq_slots, (float*)u, ldu, tokens, channels, taps);
+        return eg_launch_status();
+    }
     const unsigned blocks = (unsigned)((n + 255) / 256);
     if (dtype == EG_BF16)
         conv_silu_kernel<bf16><<<blocks, 256, 0, stream>>>((const bf16*)x, ldx, conv_w, conv_b, state, slot_floats, token_seq, seq_starts, seq_slots, (bf16*)u,
