@@ -101,7 +101,7 @@ def lasizen_bench_configs(size):
     k = {"medium": 1, "small": 2}[size]
     width, heads = 2048 // k, 16 // k
     attention = {"type": "attention", "mixer": {"heads": heads, "kv_heads": 4 // k, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "mask": {"size": 1024},
-                                                "rot": {"base": 1000000.0, "dims": 64, "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}}
+                                                "rot": {"base": 500000.0, "dims": 64, "scaling": {"factor": 4.0, "original": 8192, "fast": 32.0, "slow": 1.0}}}}
     delta = {"type": "delta", "mixer": {"heads": heads, "kv_heads": heads // 2, "dim": 128, "vdim": 128, "conv": 4}}
     mlp = {"kind": "dense", "ff": 4 * width}
     lasizen = {"architecture": "Lasizen", "vocab": 32000, "width": width, "norm": {"eps": 1e-6}, "embedding": {"scale": float(width) ** 0.5},

@@ -151,6 +151,8 @@ int eg_attention_prefill_sink(cudaStream_t stream, const void* q, int ldq, const
 int eg_attention_prefill_tcgen05_sink(cudaStream_t stream, const void* q, long long ldq, int total_tokens, const void* k_cache, const void* v_cache, const int* block_table, int table_stride, const int* positions, const int* tiles, int num_tiles, void* out, long long ldo, int num_heads, int num_kv_heads, int head_dim, int page_size, long long page_stride, long long head_stride, int num_pages, int window, float scale, int* status, int max_parts, int part_tiles, float* partial_o, float* partial_ml, int* queue, float sink_logit);
 // gemm_tcgen05.cu
 int eg_gemm_tcgen05_pair_xielu(cudaStream_t stream, const void* A, long long lda, const void* W, long long ldw, void* out, long long ldo, int M, int N, int K, int tile_n, int* status, float act_a, float act_b);
+// gemm_skinny.cu
+int eg_gemm_skinny_xielu(cudaStream_t stream, int use_pdl, const void* W, long long ldw, int M, int N, int K, const void* x, long long ldx, void* out, long long ldo, int row_blocks, int k_slices, int k_split, float* scratch, int* counters, int* status, float act_a, float act_b);
 // gated_delta.cu
 int eg_gated_delta_plan(int dk, int dv, int* rows_per_lane, int* lanes);
 // gated_delta.cu

@@ -131,6 +131,27 @@ public:
                      "gemm_skinny");
     }
 
+    // out [M, out_features] (compute dtype, from the arena) = xielu(x W^T) by the decode product, the activation on its
+    // finished sums; the caller has checked that the decode product takes the input
+    Rows skinny_xielu(const StepContext& ctx, const Rows& x, float act_a, float act_b) const {
+        const int M = x.rows, N = out_features;
+        const plans::SkinnyPlan plan = plans::skinny_plan(N, in_features, 0);
+        float* partials = nullptr;
+        int* counters = nullptr;
+        if (plan.k_split > 1) {
+            const size_t groups = (size_t)(N + plan.row_blocks * 16 - 1) / (plan.row_blocks * 16);
+            const size_t floats = (size_t)plan.k_split * groups * plan.row_blocks * 16 * plans::skinny_padded_tokens(M);
+            if (floats > KernelScratch::SKINNY_FLOATS || groups > KernelScratch::SKINNY_COUNTERS)
+                throw DeviceError("a decode product's split needs more scratch memory than the engine holds");
+            partials = ctx.scratch->skinny_partials.as<float>();
+            counters = ctx.scratch->skinny_counters.as<int>();
+        }
+        Rows out{ctx.take_rows(M, N, DType::BF16), DType::BF16, M, N, N};
+        launch_check(eg_gemm_skinny_xielu(ctx.stream, plans::use_pdl(), weight, in_features, M, N, in_features, x.p, x.ld, out.p, N, plan.row_blocks,
+                                          plan.k_slices, plan.k_split, partials, counters, ctx.status, act_a, act_b), "gemm_skinny_xielu");
+        return out;
+    }
+
     // whether with_following_norm can run for this input (the decode kernel takes it)
     bool takes_following_norm(const Rows& x) const {
         return dtype == DType::BF16 && plans::gemm_skinny_takes(dtype, x.rows, in_features) && x.rows <= plans::FUSED_NORM_MAX_TOKENS && aligned(x);

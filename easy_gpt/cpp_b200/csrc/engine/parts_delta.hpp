@@ -305,12 +305,17 @@ public:
         const int T = ctx.num_tokens;
         const DType dtype = ctx.dtype;
         const Rows h = in.pending ? in.pending->materialize() : in.rows;
-        Rows act{ctx.take_rows(T, ff_, dtype), dtype, T, ff_, ff_};
-        if (plans::gemm_tcgen05_wide_takes(dtype, T, ff_, hidden_) && Linear::aligned(h)) {
+        Rows act;
+        if (plans::gemm_skinny_takes(dtype, T, hidden_) && Linear::aligned(h)) {
+            // steps of few tokens: the decode product with the activation on its finished sums
+            act = up_.skinny_xielu(ctx, h, above_, below_);
+        } else if (plans::gemm_tcgen05_wide_takes(dtype, T, ff_, hidden_) && Linear::aligned(h)) {
+            act = Rows{ctx.take_rows(T, ff_, dtype), dtype, T, ff_, ff_};
             // prompts: the product on the tcgen05 tensor cores (CTA pairs, 256 x 256 tiles) with the activation in its epilogue
             launch_check(eg_gemm_tcgen05_pair_xielu(ctx.stream, h.p, h.ld, up_.weight, hidden_, act.p, ff_, T, ff_, hidden_, 256, ctx.status, above_, below_),
                          "gemm_tcgen05_pair_xielu");
         } else {
+            act = Rows{ctx.take_rows(T, ff_, dtype), dtype, T, ff_, ff_};
             const Rows z = up_(ctx, h, /*out_f32=*/true);
             launch_check(eg_xielu(ctx.stream, z.p, (int)z.dtype, z.ld, act.p, (int)dtype, act.ld, T, ff_, above_, below_), "xielu");
         }

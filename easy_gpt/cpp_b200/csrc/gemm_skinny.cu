@@ -90,6 +90,9 @@ struct Params {
     const float* gain_out;       //   the following norm's gain
     bf16* xn_out;                //   bfloat16(gain_out * v) [M, N]
     float* ss_out;               //   [gridDim.x][padded tokens]
+    // EPI_STORE with an activation on the way out: act(z) = act_a z^2 + z / 2 for z > 0, act_b (e^z - 1 - z) + z / 2 below
+    int act;
+    float act_a, act_b;
     const void* prefetch;        // weights of a kernel that runs soon: pulled into L2 meanwhile
     long long prefetch_bytes;
     float* scratch;              // [gridDim.y][gridDim.x][RB*16][tokens] partial sums when K is cut across CTAs
@@ -498,7 +501,8 @@ __global__ void __launch_bounds__(MAX_THREADS) skinny_kernel(const Params p) {
             const int m = e / rows_per_cta, r = e % rows_per_cta;
             const int n = n0 + r;
             if (n >= p.N) continue;
-            const float v = value(r, m);
+            float v = value(r, m);
+            if (EPI == EPI_STORE && p.act) v = v > 0.f ? fmaf(p.act_a * v, v, 0.5f * v) : fmaf(p.act_b, expm1f(v) - v, 0.5f * v);
             if (EPI == EPI_F32) p.out_f32[(size_t)m * p.ldo + n] = v;
             else p.out[(size_t)m * p.ldo + n] = __float2bfloat16_rn(v);
         }
@@ -676,15 +680,15 @@ int launch_nt(cudaStream_t stream, const Params& p, int ctas, int k_split) {
 // then need `scratch` (k_split * ceil(N / (row_blocks*16)) * row_blocks*16 * padded tokens floats) and `counters`
 // (one zeroed int per row group; left zero).  Takes M <= 64, K % 16 == 0, 32-byte aligned rows of W, 16-byte
 // aligned rows of x.  Anything else: cudaErrorInvalidValue.
-EG_API int eg_gemm_skinny(cudaStream_t stream, int epilogue, int norm, int use_pdl, const void* W, long long ldw,
-                          const float* bias, int M, int N, int K, const void* x, long long ldx, const float* resid_in,
-                          float* resid_out, const void* delta, const float* gain, float eps, void* out, long long ldo,
-                          int row_blocks, int k_slices, int k_split, float* scratch, int* counters, int num_heads,
-                          int num_kv_heads, int head_dim, const int* positions, const int* slot_map, void* k_cache,
-                          void* v_cache, const float* inv_freq, int page_size, long long page_stride,
-                          long long head_stride, long long pool_slots, int* status, const void* prefetch,
-                          long long prefetch_bytes, unsigned long long* trace, const float* ss_in, int ss_parts,
-                          float* resid_inout, const float* gain_out, void* xn_out, float* ss_out) {
+static int gemm_skinny_any(cudaStream_t stream, int epilogue, int norm, int use_pdl, const void* W, long long ldw,
+                           const float* bias, int M, int N, int K, const void* x, long long ldx, const float* resid_in,
+                           float* resid_out, const void* delta, const float* gain, float eps, void* out, long long ldo,
+                           int row_blocks, int k_slices, int k_split, float* scratch, int* counters, int num_heads,
+                           int num_kv_heads, int head_dim, const int* positions, const int* slot_map, void* k_cache,
+                           void* v_cache, const float* inv_freq, int page_size, long long page_stride,
+                           long long head_stride, long long pool_slots, int* status, const void* prefetch,
+                           long long prefetch_bytes, unsigned long long* trace, const float* ss_in, int ss_parts,
+                           float* resid_inout, const float* gain_out, void* xn_out, float* ss_out, int act, float act_a, float act_b) {
     if (M <= 0 || N <= 0) return 0;
     if (norm < 0 || norm > 2 || (norm == 2 && (!delta || !ss_in || ss_parts < 1)) ||
         (epilogue == EPI_RESID_NORM && (!resid_inout || !gain_out || !xn_out || !ss_out)))
@@ -707,6 +711,7 @@ EG_API int eg_gemm_skinny(cudaStream_t stream, int epilogue, int norm, int use_p
     p.scratch = scratch; p.counters = counters; p.trace = trace;
     p.norm_mode = norm; p.ss_in = ss_in; p.ss_parts = ss_parts;
     p.resid_inout = resid_inout; p.gain_out = gain_out; p.xn_out = (bf16*)xn_out; p.ss_out = ss_out;
+    p.act = act; p.act_a = act_a; p.act_b = act_b;
     const int ctas = (N + row_blocks * 16 - 1) / (row_blocks * 16);
 #define EG_SKINNY(E)                                                                             \
     case E: return norm == 2 ? launch_nt<E, 2>(stream, p, ctas, k_split)                          \
@@ -720,4 +725,29 @@ EG_API int eg_gemm_skinny(cudaStream_t stream, int epilogue, int norm, int use_p
         default: return (int)cudaErrorInvalidValue;
     }
 #undef EG_SKINNY
+}
+
+EG_API int eg_gemm_skinny(cudaStream_t stream, int epilogue, int norm, int use_pdl, const void* W, long long ldw,
+                          const float* bias, int M, int N, int K, const void* x, long long ldx, const float* resid_in,
+                          float* resid_out, const void* delta, const float* gain, float eps, void* out, long long ldo,
+                          int row_blocks, int k_slices, int k_split, float* scratch, int* counters, int num_heads,
+                          int num_kv_heads, int head_dim, const int* positions, const int* slot_map, void* k_cache,
+                          void* v_cache, const float* inv_freq, int page_size, long long page_stride,
+                          long long head_stride, long long pool_slots, int* status, const void* prefetch,
+                          long long prefetch_bytes, unsigned long long* trace, const float* ss_in, int ss_parts,
+                          float* resid_inout, const float* gain_out, void* xn_out, float* ss_out) {
+    return gemm_skinny_any(stream, epilogue, norm, use_pdl, W, ldw, bias, M, N, K, x, ldx, resid_in, resid_out, delta, gain, eps, out, ldo, row_blocks,
+                           k_slices, k_split, scratch, counters, num_heads, num_kv_heads, head_dim, positions, slot_map, k_cache, v_cache, inv_freq,
+                           page_size, page_stride, head_stride, pool_slots, status, prefetch, prefetch_bytes, trace, ss_in, ss_parts, resid_inout,
+                           gain_out, xn_out, ss_out, 0, 0.f, 0.f);
+}
+
+// out [M, N] bfloat16 = act(x W^T) with the xIELU activation applied to the finished sums: act(z) = act_a z^2 + z / 2 for
+// z > 0 and act_b (e^z - 1 - z) + z / 2 for z <= 0.  Sizes, plan and scratch as eg_gemm_skinny with a plain store.
+EG_API int eg_gemm_skinny_xielu(cudaStream_t stream, int use_pdl, const void* W, long long ldw, int M, int N, int K, const void* x, long long ldx,
+                                void* out, long long ldo, int row_blocks, int k_slices, int k_split, float* scratch, int* counters, int* status,
+                                float act_a, float act_b) {
+    return gemm_skinny_any(stream, EPI_STORE, 0, use_pdl, W, ldw, nullptr, M, N, K, x, ldx, nullptr, nullptr, nullptr, nullptr, 0.f, out, ldo, row_blocks,
+                           k_slices, k_split, scratch, counters, 0, 0, 0, nullptr, nullptr, nullptr, nullptr, nullptr, 0, 0, 0, 0, status, nullptr, 0,
+                           nullptr, nullptr, 0, nullptr, nullptr, nullptr, nullptr, 1, act_a, act_b);
 }

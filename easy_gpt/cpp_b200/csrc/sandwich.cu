@@ -178,34 +178,45 @@ __global__ void __launch_bounds__(256) rmsnorm_shift_warp_kernel(const float* __
                                                                  const float* __restrict__ mu, float* __restrict__ state, long long slot_floats,
                                                                  const int* __restrict__ token_seq, const int* __restrict__ seq_starts,
                                                                  const int* __restrict__ seq_slots, TO* __restrict__ out, int tokens, int hidden) {
-    const int lane = threadIdx.x & 31;
-    const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (t >= tokens) return;
+    __shared__ float inv_of_warp[8];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int t = blockIdx.x * (blockDim.x >> 5) + warp;
+    const bool live = t < tokens;
     const int quads = hidden / 4;
-    const int seq = token_seq[t], start = seq_starts[seq];
-    const bool first = t == start;
-    float* slot = state + (size_t)seq_slots[seq] * slot_floats;
-    const float* x = stream + (size_t)t * hidden;
-    // the row in front, normed again here; the first token's warp norms the entry's last row for the slot instead
-    const float* other = stream + (size_t)(first ? seq_starts[seq + 1] - 1 : t - 1) * hidden;
-    // the own row stays in registers; the other one is read twice (the second time from the cache), so that a warp holds
-    // one row and many warps fit an SM
+    const int seq = live ? token_seq[t] : 0, start = live ? seq_starts[seq] : 0;
+    const bool first = live && t == start;
+    float* slot = state + (size_t)(live ? seq_slots[seq] : 0) * slot_floats;
+    const float* x = stream + (size_t)(live ? t : 0) * hidden;
+    // the row in front; the first token's warp norms the entry's last row for the slot instead
+    const float* other = stream + (size_t)(live ? (first ? seq_starts[seq + 1] - 1 : t - 1) : 0) * hidden;
+    // The own row stays in registers.  The inverse root mean square of the row in front is the warp in front's own (through
+    // shared memory: the same instructions in the same order, so the same bits as when this warp computes it); only a
+    // block's first warp and an entry's first token sum the other row's squares themselves.
     float4 v[VPL];
     float ss = 0.f, so = 0.f;
 #pragma unroll
     for (int i = 0; i < VPL; ++i) {
         const int q = i * 32 + lane;
-        v[i] = q < quads ? load4(x, q) : make_float4(0.f, 0.f, 0.f, 0.f);
+        v[i] = live && q < quads ? load4(x, q) : make_float4(0.f, 0.f, 0.f, 0.f);
     }
+    const bool own_sum = live && (first || warp == 0);
 #pragma unroll
     for (int i = 0; i < VPL; ++i) {
         const int q = i * 32 + lane;
         ss += squares(v[i]);
-        if (q < quads) so += squares(load4(other, q));
+        if (own_sum && q < quads) so += squares(load4(other, q));
     }
     ss = warp_sum(ss);
-    so = warp_sum(so);
-    const float inv = 1.0f / sqrtf(ss / (float)hidden + eps), inv_other = 1.0f / sqrtf(so / (float)hidden + eps);
+    const float inv = 1.0f / sqrtf(ss / (float)hidden + eps);
+    if (lane == 0) inv_of_warp[warp] = inv;
+    float inv_other = 0.f;
+    if (own_sum) {
+        so = warp_sum(so);
+        inv_other = 1.0f / sqrtf(so / (float)hidden + eps);
+    }
+    __syncthreads();
+    if (!live) return;
+    if (!own_sum) inv_other = inv_of_warp[warp - 1];
 #pragma unroll
     for (int i = 0; i < VPL; ++i) {
         const int q = i * 32 + lane;

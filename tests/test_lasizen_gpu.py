@@ -69,7 +69,7 @@ ALONE = {
     "attention": model([(attention(), None)]),
     "attention_all_keys": model([(attention(window=None), None)]),
     "attention_no_rotation": model([(attention(rot_dims=None), None)]),
-    "attention_wide": model([(attention(heads=8, kv_heads=2, dim=64, vdim=32, scale=0.125, window=40, rot_dims=32, base=1e6, scaling=(8.0, 2048, 32.0, 1.0)), None)], width=128),
+    "attention_wide": model([(attention(heads=8, kv_heads=2, dim=64, vdim=48, scale=0.11, window=40, rot_dims=24, base=5e5, scaling=(6.0, 1024, 24.0, 2.0)), None)], width=128),
     # key and value sizes equal: keys and values in planes of their own, which the tensor-core kernels read in bfloat16
     "attention_planes_64": model([(attention(heads=4, kv_heads=2, dim=64, vdim=64, scale=0.125, window=40, rot_dims=32), None)], width=128),
     "attention_planes_128": model([(attention(heads=2, kv_heads=1, dim=128, vdim=128, scale=0.09, window=None, rot_dims=64, scaling=None), None)], width=128),
