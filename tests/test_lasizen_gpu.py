@@ -74,6 +74,10 @@ ALONE = {
     "attention_planes_64": model([(attention(heads=4, kv_heads=2, dim=64, vdim=64, scale=0.125, window=40, rot_dims=32), None)], width=128),
     "attention_planes_128": model([(attention(heads=2, kv_heads=1, dim=128, vdim=128, scale=0.09, window=None, rot_dims=64, scaling=None), None)], width=128),
     "attention_planes_32": model([(attention(heads=6, kv_heads=3, dim=32, vdim=32, scale=0.2, window=33, rot_dims=8), 64)]),
+    "attention_planes_256": model([(attention(heads=2, kv_heads=2, dim=256, vdim=256, scale=0.06, window=45, rot_dims=128, scaling=None), None)], width=96),
+    # a width that is no multiple of four, sizes that are no multiples of four either
+    "odd_width": model([(attention(heads=3, kv_heads=1, dim=10, vdim=6, scale=0.4, window=9, rot_dims=4), 27), (delta(heads=2, kv_heads=1, dim=6, vdim=10, conv=3), None)],
+                       width=90, vocab=53),
     "attention_large_values": model([(attention(heads=2, kv_heads=1, dim=24, vdim=136, scale=0.25, window=50), None)]),
     "delta": model([(delta(), None)]),
     "delta_wide": model([(delta(heads=4, kv_heads=2, dim=128, vdim=64, conv=4), None)], width=128),
@@ -138,7 +142,8 @@ def test_residual_stream_after_every_layer_run():
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name,cfg", [("general", GENERAL), ("odd", ODD), ("ones", ONES), ("alone_attention_wide", None), ("alone_delta_wide", None),
                                       ("alone_delta_long_keys", None), ("alone_attention_large_values", None), ("alone_attention_planes_64", None),
-                                      ("alone_attention_planes_128", None), ("alone_attention_planes_32", None)])
+                                      ("alone_attention_planes_128", None), ("alone_attention_planes_32", None), ("alone_attention_planes_256", None),
+                                      ("alone_odd_width", None)])
 def test_prompt_whole_and_token_by_token(folders, name, cfg, dtype):
     if cfg is None:
         name = name[len("alone_"):]
